@@ -23,6 +23,22 @@ class ModelConfigC(ctypes.Structure):
                 ("page_size", ctypes.c_int), ("tp_rank", ctypes.c_int), ("tp_size", ctypes.c_int)]
 
 
+class MezilixLayerC(ctypes.Structure):
+    """mirror of ``asd_mezilix_layer_config``"""
+    _fields_ = [("heads", ctypes.c_int), ("dim", ctypes.c_int), ("rot_dim", ctypes.c_int), ("vdim", ctypes.c_int),
+                ("kv_rank", ctypes.c_int), ("rot_dims", ctypes.c_int), ("window", ctypes.c_int),
+                ("rot_base", ctypes.c_float), ("scale", ctypes.c_float), ("experts", ctypes.c_int),
+                ("top", ctypes.c_int), ("ff", ctypes.c_int)]
+
+
+class MezilixConfigC(ctypes.Structure):
+    """mirror of ``asd_mezilix_config``"""
+    _fields_ = [("width", ctypes.c_int), ("vocab", ctypes.c_int), ("n_layers", ctypes.c_int), ("eps", ctypes.c_float),
+                ("buckets", ctypes.c_int), ("mul_prev", ctypes.c_int), ("mul_cur", ctypes.c_int),
+                ("max_tokens", ctypes.c_int), ("page_size", ctypes.c_int), ("ring", ctypes.c_int),
+                ("dtype", ctypes.c_int)]
+
+
 def library_path() -> str:
     return os.path.join(_HERE, "libasd_b200.so")
 
@@ -74,9 +90,20 @@ def lib() -> ctypes.CDLL:
         "asd_debug_gemm_trace": (i32, [vp, i32]),
         "asd_debug_attn_trace": (i32, [vp, i32]),
         "asd_engine_forward": (i32, [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, vp, i32, vp, c.c_longlong, vp]),
+        "asd_mezilix_create": (vp, [vp, vp]),
+        "asd_mezilix_destroy": (None, [vp]),
+        "asd_mezilix_set_globals": (i32, [vp, vp, vp, vp, vp]),
+        "asd_mezilix_set_layer": (i32, [vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
+        "asd_mezilix_cache_bytes": (sz, [vp, i32]),
+        "asd_mezilix_set_cache": (i32, [vp, vp, i32, vp, i32, i32, vp, vp]),
+        "asd_mezilix_set_option": (i32, [vp, c.c_char_p, i32]),
+        "asd_mezilix_forward": (i32, [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, vp, i32, vp, c.c_longlong, vp, vp]),
+        "asd_linear_simt": (i32, [vp, i32, vp, i32, vp, i32, i32, i32, i32, vp]),
     }
     for name, (res, args) in sigs.items():
-        fn = getattr(L, name)
+        fn = getattr(L, name, None)
+        if fn is None:       # a library built with only some components (build.py) lacks the others' entry points
+            continue
         fn.restype = res
         fn.argtypes = args
     _LIB = L

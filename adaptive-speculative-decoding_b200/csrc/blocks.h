@@ -1,0 +1,114 @@
+// Host-side launchers of the sequence-model building blocks that take their sizes and constants as arguments
+// (linear_simt.cu, stream_ops.cu, latent_attention.cu, moe.cu).  An engine (mezilix_engine.cu) strings them together;
+// none of them knows a model.  `f32` flags select the element type of a buffer: 0 = bf16, 1 = fp32.  Norms, scores,
+// softmax weights, router probabilities, the residual stream and the carried state are fp32 in both modes.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace asd {
+
+// ---------------------------------------------------------------------------------------------- linear_simt.cu
+// C[z][m][n] = epilogue( sum_k A[z][m][k] * W[z][n][k] ), fp32 FMA accumulation in increasing k (no tensor cores, no
+// reduced-precision mode): the exact path of the fp32 engines and the fallback for shapes the tcgen05 GEMM refuses.
+// A row of the result depends on nothing but its own A row, so it is identical however the rows are batched.
+struct SimtLinear {
+    const void* a = nullptr;  // element (z, m, k) at a + z * a_zs + row(m) * lda + k
+    const void* w = nullptr;  // w_kn == 0: (z, n, k) at w + z * w_zs + n * ldw + k;  w_kn == 1: at w + z * w_zs + k * ldw + n
+    void* c = nullptr;        // (z, m, n) at c + z * c_zs + m * ldc + n
+    long long lda = 0, ldw = 0, ldc = 0, a_zs = 0, w_zs = 0, c_zs = 0;
+    int a_f32 = 0, w_f32 = 0, c_f32 = 1, w_kn = 0;
+    int M = 0, N = 0, K = 0, Z = 1;
+    // grouped form (mixture of experts): rows of batch z are [group_off[z], group_off[z + 1]) of A and C (device array,
+    // M = upper bound of rows per group, a_zs and c_zs ignored); gather (optional) maps such a row to its row of A
+    const int* group_off = nullptr;
+    const int* gather = nullptr;
+    int epilogue = 0;         // 0 none, 1 relu(x)^2
+};
+int launch_simt_linear(const SimtLinear& L, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------- stream_ops.cu
+// Carried per-sequence state: rings of `ring` entries indexed by position % ring, so that a caller that re-feeds the
+// last few positions (speculative verification after a rejected tail) finds the state of any of them.
+struct SeqIndex {
+    const int* tokens;      // [M]
+    const int* positions;   // [M]
+    const int* token_slot;  // [M]
+    int M;
+};
+// x0[m] = embed[token] + pair_table[(prev * mul_prev + token * mul_cur) % buckets] (row `buckets` at position 0), fp32;
+// prev = the token one row up if that row is the same sequence's previous position, else tok_ring[slot][(pos-1) % ring].
+// Also writes hn = x0 / rms(x0) * g (the first layer's scalar-gain RMS norm, fp32).
+int launch_embed_pair(const SeqIndex& ix, const void* embed, const void* pair_table, int wf32, int buckets, int mul_prev,
+                      int mul_cur, const int* tok_ring, int ring, float* x0, const void* g, float eps, float* hn, int D,
+                      cudaStream_t stream);
+// tok_ring[slot][pos % ring] = token for the last `ring` tokens of every run (after launch_embed_pair has read it)
+int launch_commit_tokens(const SeqIndex& ix, int* tok_ring, int ring, cudaStream_t stream);
+// Token shift: mixed = hn + (hn_prev - hn) * mu, hn_prev = the previous position's UNSHIFTED hn (row above, else
+// state ring, zeros at position 0).  Writes h = hn and hs = mixed in the engine's element type.
+int launch_token_shift(const SeqIndex& ix, const float* hn, const float* state_ring, int ring, const void* mu, int wf32,
+                       void* h, void* hs, int of32, int D, cudaStream_t stream);
+int launch_commit_shift_state(const SeqIndex& ix, const float* hn, float* state_ring, int ring, int D, cudaStream_t stream);
+// Parallel-layer close with depth-weighted averaging of all earlier results:
+//   X[i+1] = x_in + mix + sum_k gate[m][k] * expert_out[slot_of[m][k]]      (no expert term if top == 0)
+//   x_next = sum_{j <= i+1} coeff[j] * X[j];  hn = x_next / rms(x_next) * g_next
+// X is the stack [layers + 1][stack_stride] of fp32 [M][D] results (X[0] = embedding output); x_in may alias x_next.
+struct LayerClose {
+    const float* x_in;
+    const float* mix;          // [M][D]
+    const float* expert_out;   // [M * top][D] rows by slot
+    const int* slot_of;        // [M][top]
+    const float* gate;         // [M][top]
+    int top;
+    float* stack;
+    size_t stack_stride;
+    int layer;                 // i
+    const void* coeff;         // [i + 2]
+    const void* g_next;        // scalar gain of the norm that follows
+    int wf32;
+    float eps;
+    float* x_next;
+    float* hn;
+    int M, D;
+};
+int launch_layer_close(const LayerClose& L, cudaStream_t stream);
+// dst[r] = src[rows[r]] converted to the engine's element type (rows == nullptr: identity)
+int launch_select_rows(const float* src, const int* rows, void* dst, int of32, int n, int D, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------- latent_attention.cu
+// Latent (low-rank) key/value attention with one shared rotated key part, evaluated in latent space: the cache holds
+// per position [R latent | dr rotated key] and a query is first carried through the key up-projection, so that
+//   score = scale * (q_lat . c + q_rot . k_rot),  out_lat = softmax . c,  and the value up-projection follows.
+struct LatentDims {
+    int heads, dn, dr, dv, R;   // per head: dn unrotated + dr rotated query dims, dv value dims; R latent size
+    int rot_dims;               // leading coordinates of the rotated part that rotate (pairs i, i + rot_dims / 2)
+    int window;                 // position p sees p - window < j <= p
+    float scale;
+};
+struct PagedRows {
+    void* pool;                // this layer's rows: [num_pages][page_size][row_elems]
+    int f32;
+    const int* page_table;     // [slots][max_pages]
+    int max_pages, page_size;
+};
+// qd fp32 [M][heads * (dn + dr) + R + dr] = (queries head by head | latent | rotated key).  RMS-norms the latent (vector
+// weight), rotates the key part and appends both to the paged cache; rotates every head's query part into
+// q_lat[m][head][R .. R + dr) (fp32, row length R + dr).  inv_freq fp32 [rot_dims / 2].
+int launch_latent_post(const SeqIndex& ix, const float* qd, const LatentDims& d, const void* c_norm, int wf32, float eps,
+                       const float* inv_freq, const PagedRows& cache, float* q_lat, cudaStream_t stream);
+// out_lat fp32 [M][heads][R].  cu_q / seq_slot as in asd_engine_forward; a sequence's tokens are consecutive positions.
+int launch_latent_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen,
+                            const float* q_lat, const LatentDims& d, const PagedRows& cache, float* out_lat,
+                            cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------- moe.cu
+// Router: probs = softmax(logits) over all E experts (fp32); the `top` largest are kept with their probabilities as
+// gates (not renormalised; ties go to the lower index).  Then the (token, choice) pairs are grouped by expert:
+// group_off [E + 1], sorted_tok [M * top] (token of each slot), slot_of [M][top].  counters: int [2 E + 1] scratch.
+int launch_moe_route(const float* logits, int M, int E, int top, int* expert_of, float* gate, int* counters,
+                     int* group_off, int* sorted_tok, int* slot_of, cudaStream_t stream);
+
+int preload_blocks();
+
+}  // namespace asd

@@ -10,7 +10,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ._lib import AsdError, ModelConfigC, check, lib
+from ._lib import AsdError, MezilixConfigC, MezilixLayerC, ModelConfigC, check, lib
 from .models.qwen2 import Qwen2Config, pack_layer, random_packed_layer
 from .ops import NUM_FEATURES
 
@@ -19,9 +19,122 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class PageTable:
+    """Slots and pages of a paged cache: ``table`` int32 [max_seqs, max_pages] on the device maps (sequence slot,
+    position // page_size) to a page of the pool.
+
+    Static form (``dynamic=False``): every slot owns ``max_pages`` pages from the start, deliberately shuffled so
+    that the indirection is always live; nothing is ever allocated or freed (uniform benchmark batches).
+    Dynamic form: pages come from a free list when ``reserve(slot, n_tokens)`` grows a sequence and go back with
+    ``release(slot)``; slots are handed out by ``alloc_slot`` / given back by ``free_slot``.  The host keeps the
+    mirror; only the changed cells are copied to the device (ordered on the current stream before the next forward)."""
+
+    def __init__(self, max_seqs: int, max_pages: int, page_size: int, device, num_pages: Optional[int] = None,
+                 dynamic: bool = False, shuffle: bool = True, seed: int = 1234):
+        self.max_seqs, self.max_pages, self.page_size, self.dynamic = max_seqs, max_pages, page_size, dynamic
+        self.num_pages = max_pages * max_seqs if (num_pages is None or not dynamic) else int(num_pages)
+        ids = torch.arange(self.num_pages, dtype=torch.int32)
+        if shuffle:
+            ids = ids[torch.randperm(self.num_pages, generator=torch.Generator().manual_seed(seed))]
+        if dynamic:
+            self.free_pages = ids.tolist()
+            self.free_slots = list(range(max_seqs - 1, -1, -1))
+            self.owned = [[] for _ in range(max_seqs)]
+            self.table = torch.zeros(max_seqs, max_pages, dtype=torch.int32, device=device)
+        else:
+            self.table = ids.view(max_seqs, max_pages).contiguous().to(device)
+
+    def alloc_slot(self) -> int:
+        if not self.dynamic:
+            raise AsdError("a static page table hands out no slots")
+        if not self.free_slots:
+            raise AsdError(f"all {self.max_seqs} sequence slots are in use")
+        return self.free_slots.pop()
+
+    def reserve(self, slot: int, n_tokens: int) -> None:
+        """make positions 0 .. n_tokens - 1 of ``slot`` addressable"""
+        need = (n_tokens + self.page_size - 1) // self.page_size
+        if need > self.max_pages:
+            raise AsdError(f"{n_tokens} tokens exceed the per-sequence limit {self.max_pages * self.page_size}")
+        if not self.dynamic:
+            return
+        have = len(self.owned[slot])
+        if need <= have:
+            return
+        if need - have > len(self.free_pages):
+            raise AsdError(f"cache exhausted: {need - have} pages wanted, {len(self.free_pages)} free")
+        new = [self.free_pages.pop() for _ in range(need - have)]
+        self.owned[slot] += new
+        self.table[slot, have:need] = torch.tensor(new, dtype=torch.int32).to(self.table.device, non_blocking=True)
+
+    def release(self, slot: int) -> None:
+        """give the slot's pages back (their contents stay until the next owner overwrites them)"""
+        if self.dynamic:
+            self.free_pages += reversed(self.owned[slot])
+            self.owned[slot] = []
+
+    def free_slot(self, slot: int) -> None:
+        self.release(slot)
+        if self.dynamic:
+            self.free_slots.append(slot)
+
+    def pages_in_use(self) -> int:
+        return sum(len(o) for o in self.owned) if self.dynamic else self.num_pages
+
+
 class _BatchOps:
     """Uniform-batch / prefill helpers shared by ``QwenEngine`` and ``TPQwenEngine`` (anything with ``forward``,
     ``device``, ``cfg``, ``max_tokens`` and an ``_index_cache`` dict)."""
+
+    def max_qlen(self) -> int:
+        """most new positions of one sequence in one forward (the grouped-query attention kernels put q_len x group
+        query rows on 128 lanes)"""
+        return max(1, 128 // (self.cfg.num_attention_heads // self.cfg.num_key_value_heads))
+
+    def forward_ragged(self, items, device=None, layer_out: bool = False):
+        """One scheduler step over requests of unequal length: ``items`` = [(slot, start_pos, token ids, wanted
+        indices)], every request's tokens continuing at ``start_pos`` from what the cache and state hold.  Runs as few
+        forwards as ``max_tokens`` / ``max_qlen`` allow (a request is cut wherever a forward is full), and returns the
+        fp32 logits of the wanted places in the order of the items [n_wanted, V] (None if nothing is wanted)."""
+        dev = torch.device(device) if device is not None else self.device
+        per_seq, cap = self.max_qlen(), self.max_tokens
+        n_want = sum(len(it[3]) for it in items)
+        out = torch.empty(n_want, self.cfg.vocab_size, dtype=torch.float32, device=dev) if n_want else None
+        streams = []
+        done = [0] * len(items)
+        base, b = [], 0
+        for it in items:
+            base.append(b)
+            b += len(it[3])
+        while any(done[i] < len(it[2]) for i, it in enumerate(items)):
+            toks, pos, tslot, cu, sslot, rows, dest = [], [], [], [0], [], [], []
+            qmax = kvmax = 0
+            for i, (slot, start, ids, want) in enumerate(items):
+                a = done[i]
+                n = min(len(ids) - a, per_seq, cap - len(toks))
+                if n <= 0:
+                    continue
+                for j, wi in enumerate(want):
+                    if a <= wi < a + n:
+                        rows.append(len(toks) + wi - a)
+                        dest.append(base[i] + j)
+                toks += ids[a:a + n]
+                pos += range(start + a, start + a + n)
+                tslot += [slot] * n
+                cu.append(len(toks))
+                sslot.append(slot)
+                qmax, kvmax = max(qmax, n), max(kvmax, start + a + n)
+                done[i] = a + n
+            mk = lambda x: torch.tensor(x, dtype=torch.int32).to(dev, non_blocking=True)
+            kw = {"layer_out": True} if layer_out else {}
+            lg = self.forward(mk(toks), mk(pos), mk(tslot), mk(cu), mk(sslot), qmax, kvmax, mk(rows) if rows else None,
+                              None, bool(rows), **kw)
+            if layer_out:
+                lg, st = lg
+                streams.append(st)
+            if rows:
+                out[torch.tensor(dest, device=dev)] = lg
+        return (out, streams) if layer_out else out
 
     def _uniform_index(self, nseq: int, q: int):
         """static index tensors of a uniform (nseq x q) call, built once per shape"""
@@ -57,9 +170,8 @@ class _BatchOps:
     def prefill(self, prompt_ids: torch.Tensor, slots: torch.Tensor, chunk: int = 0, want_logits: bool = True):
         """Chunked prefill of equal-length prompts [nseq, P]; returns the logits of the last position."""
         nseq, P = prompt_ids.shape
-        G = self.cfg.num_attention_heads // self.cfg.num_key_value_heads
         if chunk <= 0:
-            chunk = max(1, min(128 // G, self.max_tokens // nseq))
+            chunk = max(1, min(self.max_qlen(), self.max_tokens // nseq))
         logits = None
         zero = torch.zeros(nseq, dtype=torch.int32, device=prompt_ids.device)
         for s in range(0, P, chunk):
@@ -78,9 +190,8 @@ class _BatchOps:
         nseq = len(prompts)
         lens = [len(p) for p in prompts]
         assert nseq == slots.numel() and min(lens) >= 1
-        G = self.cfg.num_attention_heads // self.cfg.num_key_value_heads
         if chunk <= 0:
-            chunk = max(1, min(128 // G, self.max_tokens // nseq))
+            chunk = max(1, min(self.max_qlen(), self.max_tokens // nseq))
         out = torch.empty(nseq, self.cfg.vocab_size, dtype=torch.float32, device=dev)
         slots_h = slots.cpu().tolist()
         for s0 in range(0, max(lens), chunk):
@@ -129,13 +240,12 @@ class QwenEngine(_BatchOps):
         if not self.h:
             check(-1, "asd_engine_create")
         self.max_pages = (max_seq_len + page_size - 1) // page_size
-        self.num_pages = self.max_pages * max_seqs
+        # pages of a sequence are deliberately NOT contiguous: the indirection is always live
+        self.pages = PageTable(max_seqs, self.max_pages, page_size, self.device, shuffle=shuffle_pages)
+        self.num_pages = self.pages.num_pages
         nbytes = lib().asd_engine_kv_pool_bytes(ctypes.byref(self.c), self.num_pages)
         self.kv_pool = torch.zeros(nbytes // 2, dtype=torch.bfloat16, device=self.device)
-        ids = torch.arange(self.num_pages, dtype=torch.int32)
-        if shuffle_pages:  # pages of a sequence are deliberately NOT contiguous: the indirection is always live
-            ids = ids[torch.randperm(self.num_pages, generator=torch.Generator().manual_seed(1234))]
-        self.page_table = ids.view(max_seqs, self.max_pages).contiguous().to(self.device)
+        self.page_table = self.pages.table
         check(lib().asd_engine_set_kv(self.h, self.kv_pool.data_ptr(), self.num_pages, self.page_table.data_ptr(),
                                       max_seqs, self.max_pages), "asd_engine_set_kv")
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, dtype=torch.int64).float() / cfg.head_dim))
@@ -178,6 +288,8 @@ class QwenEngine(_BatchOps):
         head = embed if "lm_head.weight" not in w else dev(w["lm_head.weight"])
         self._set_globals(embed, dev(w["model.norm.weight"]), head)
         return self
+
+    load_weights = load_hf_weights     # the name every engine answers to (Stage, trace runner)
 
     def load_random(self, seed: int, std: float = 0.02):
         """Random-init weights generated directly in the engine layout (full-size benchmarks)."""
@@ -304,6 +416,145 @@ def _remote_forward(eng, dev, tokens, positions, token_slot, cu_q, seq_slot, max
         done.record(side)
     torch.cuda.current_stream(src).wait_event(done)
     return logits_out if n_rows else None
+
+
+class MezilixEngine(_BatchOps):
+    """One Mezilix-family model on one GPU: wraps an ``asd_mezilix_engine_t`` handle and owns what a sequence carries
+    between forwards: the paged latent cache (``PageTable``; dynamic by default, static for uniform benchmark
+    batches), the ring of recent tokens (the embedding hashes the previous token) and, per layer, the ring of recent
+    normed inputs (token shift).  The rings are indexed by position % ring, so re-feeding any of the last ``ring``
+    positions - what speculative verification does after a rejected tail - finds the right state.
+    ``dtype``: torch.bfloat16 (bf16 weights / cache / matrix inputs, fp32 accumulation) or torch.float32 (true fp32
+    everywhere).  Same ``forward`` contract as ``QwenEngine``, so ``SpecDecoder`` and ``Stage`` drive it unchanged."""
+
+    def __init__(self, cfg, max_seqs: int, max_seq_len: int, max_tokens: int = 1024, page_size: int = 16,
+                 device="cuda", dtype=torch.bfloat16, ring: int = 8, num_pages: Optional[int] = None,
+                 dynamic_pages: bool = False, shuffle_pages: bool = True):
+        if not torch.cuda.is_available():
+            raise AsdError("MezilixEngine needs a CUDA device (there is no CPU fallback)")
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise AsdError(f"MezilixEngine runs in bfloat16 or float32, not {dtype}")
+        dev = torch.device(device)
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        self.cfg, self.device, self.dtype = cfg, dev, dtype
+        self.tp_rank, self.tp_size = 0, 1
+        self.max_seqs, self.max_seq_len, self.max_tokens, self.page_size = max_seqs, max_seq_len, max_tokens, page_size
+        self.ring = int(ring)
+        self.c = MezilixConfigC(cfg.width, cfg.vocab_size, cfg.num_hidden_layers, cfg.eps, cfg.buckets, cfg.mul_prev,
+                                cfg.mul_cur, max_tokens, page_size, self.ring, 1 if dtype == torch.float32 else 0)
+        arr = (MezilixLayerC * max(1, cfg.num_hidden_layers))()
+        for i, l in enumerate(cfg.layers):
+            arr[i] = MezilixLayerC(l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.window, l.rot_base,
+                                   l.scale, l.experts, l.top, l.ff)
+        self._lock = threading.Lock()
+        with torch.cuda.device(self.device):
+            self.h = lib().asd_mezilix_create(ctypes.byref(self.c), arr)
+        if not self.h:
+            check(-1, "asd_mezilix_create")
+        self.max_pages = (max_seq_len + page_size - 1) // page_size
+        self.pages = PageTable(max_seqs, self.max_pages, page_size, self.device, num_pages=num_pages,
+                               dynamic=dynamic_pages, shuffle=shuffle_pages)
+        self.num_pages = self.pages.num_pages
+        nbytes = lib().asd_mezilix_cache_bytes(self.h, self.num_pages)
+        self.cache_pool = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=self.device)
+        self.token_ring = torch.zeros(max_seqs, self.ring, dtype=torch.int32, device=self.device)
+        self.shift_ring = torch.zeros(max(1, cfg.num_hidden_layers), max_seqs, self.ring, cfg.width, dtype=torch.float32,
+                                      device=self.device)
+        check(lib().asd_mezilix_set_cache(self.h, self.cache_pool.data_ptr(), self.num_pages, self.pages.table.data_ptr(),
+                                          max_seqs, self.max_pages, self.token_ring.data_ptr(),
+                                          self.shift_ring.data_ptr()), "asd_mezilix_set_cache")
+        self._weights = []
+        self._index_cache = {}
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().asd_mezilix_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def max_qlen(self) -> int:
+        return self.max_tokens          # the latent attention kernel tiles any number of new positions
+
+    # ------------------------------------------------------------------ weights
+    def load_weights(self, w: Dict[str, torch.Tensor]):
+        """state dict with the checkpoint's tensor names (any device, any float type) -> engine layout"""
+        from .models.mezilix import pack_layer as pack
+        dev = lambda t: t.to(device=self.device, dtype=self.dtype).contiguous()
+        for i in range(self.cfg.num_hidden_layers):
+            t = pack(w, self.cfg, i, self.device, self.dtype)
+            self._weights.append(t)
+            ptr = lambda k: None if t[k] is None else t[k].data_ptr()
+            check(lib().asd_mezilix_set_layer(self.h, i, ptr("gain"), ptr("shift"), ptr("coeff"), ptr("wqd"),
+                                              ptr("latent_gain"), ptr("wuk"), ptr("wuv"), ptr("wo"), ptr("router"),
+                                              ptr("w_up"), ptr("w_down")), "asd_mezilix_set_layer")
+        for k, shape in (("embed", (self.cfg.vocab_size, self.cfg.width)),
+                         ("bigram", (self.cfg.buckets + 1, self.cfg.width)), ("head", (self.cfg.vocab_size, self.cfg.width))):
+            if k not in w or tuple(w[k].shape) != shape:
+                raise AsdError(f"tensor {k}: expected shape {shape}, got {tuple(w[k].shape) if k in w else None}")
+        g = (dev(w["embed"]), dev(w["bigram"]), dev(w["final.norm"].reshape(1)), dev(w["head"]))
+        self._weights.append(g)
+        check(lib().asd_mezilix_set_globals(self.h, *[x.data_ptr() for x in g]), "asd_mezilix_set_globals")
+        return self
+
+    load_hf_weights = load_weights
+
+    def load_random(self, seed: int, std: float = 0.02):
+        from .models.mezilix import random_weights
+        return self.load_weights(random_weights(self.cfg, seed, device=self.device))
+
+    def set_option(self, name: str, value: int):
+        check(lib().asd_mezilix_set_option(self.h, name.encode(), int(value)), "asd_mezilix_set_option")
+
+    # ------------------------------------------------------------------ sequences
+    def open_sequence(self) -> int:
+        """a free slot (dynamic page table); its first forward starts at position 0, which resets the carried state"""
+        return self.pages.alloc_slot()
+
+    def close_sequence(self, slot: int) -> None:
+        self.pages.free_slot(slot)
+
+    def reserve(self, slot: int, n_tokens: int) -> None:
+        if n_tokens > self.max_seq_len:
+            raise AsdError(f"sequence of {n_tokens} tokens exceeds max_seq_len {self.max_seq_len}")
+        self.pages.reserve(slot, n_tokens)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, tokens, positions, token_slot, cu_q, seq_slot, max_qlen: int, max_kv_len: int,
+                logit_rows: Optional[torch.Tensor] = None, logits_out: Optional[torch.Tensor] = None,
+                want_logits: bool = True, logits_ld: int = 0, layer_out: bool = False):
+        """int32 CUDA tensors on this engine's device; returns fp32 logits [rows, vocab] (or None).  With
+        ``layer_out`` also the stream that leaves every layer, fp32 [layers, M, width]."""
+        M, nseq = tokens.numel(), seq_slot.numel()
+        for t in (tokens, positions, token_slot, cu_q, seq_slot):
+            assert t.dtype == torch.int32 and t.is_contiguous() and t.is_cuda, "int32 contiguous CUDA tensors"
+            if t.device != self.device:
+                raise AsdError("MezilixEngine.forward: inputs must live on the engine's device")
+        if max_kv_len > self.max_pages * self.page_size:
+            raise AsdError(f"sequence length bound {max_kv_len} exceeds this engine's max_seq_len "
+                           f"{self.max_pages * self.page_size} (page-table overrun refused)")
+        n_rows = 0 if not want_logits else (M if logit_rows is None else logit_rows.numel())
+        if n_rows and logits_out is None:
+            logits_out = torch.empty(n_rows, self.cfg.vocab_size, dtype=torch.float32, device=self.device)
+        if n_rows and logits_out.device != self.device:
+            raise AsdError("logits_out must live on the engine's device")
+        streams = (torch.empty(self.cfg.num_hidden_layers, M, self.cfg.width, dtype=torch.float32, device=self.device)
+                   if layer_out else None)
+        with self._lock, torch.cuda.device(self.device):
+            rc = lib().asd_mezilix_forward(
+                self.h, tokens.data_ptr(), positions.data_ptr(), token_slot.data_ptr(), M, cu_q.data_ptr(),
+                seq_slot.data_ptr(), nseq, max_qlen, max_kv_len,
+                None if logit_rows is None else logit_rows.data_ptr(), n_rows,
+                None if not n_rows else logits_out.data_ptr(), logits_ld,
+                None if streams is None else streams.data_ptr(), _stream())
+        check(rc, "asd_mezilix_forward")
+        res = logits_out if n_rows else None
+        return (res, streams) if layer_out else res
 
 
 class TPQwenEngine(_BatchOps):

@@ -180,7 +180,8 @@ def load_safetensors_dir(path: str) -> Dict[str, torch.Tensor]:
     files = sorted(glob.glob(os.path.join(path, "*.safetensors")))
     if not files:
         raise FileNotFoundError(f"no *.safetensors under {path}")
-    dtypes = {"BF16": (torch.bfloat16, 2), "F16": (torch.float16, 2), "F32": (torch.float32, 4)}
+    dtypes = {"BF16": (torch.bfloat16, 2), "F16": (torch.float16, 2), "F32": (torch.float32, 4), "I32": (torch.int32, 4),
+              "I64": (torch.int64, 8)}
     out: Dict[str, torch.Tensor] = {}
     for fn in files:
         with open(fn, "rb") as f:
@@ -204,7 +205,7 @@ def save_safetensors(w: Dict[str, torch.Tensor], filename: str) -> None:
     """inverse of ``load_safetensors_dir`` for one shard (tests, tools)"""
     import json
     import struct
-    names = {torch.bfloat16: "BF16", torch.float16: "F16", torch.float32: "F32"}
+    names = {torch.bfloat16: "BF16", torch.float16: "F16", torch.float32: "F32", torch.int32: "I32", torch.int64: "I64"}
     header, blobs, off = {}, [], 0
     for k, t in w.items():
         t = t.contiguous().cpu()

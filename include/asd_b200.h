@@ -240,6 +240,67 @@ ASD_API int asd_engine_forward(asd_engine_t* e, const int32_t* tokens, const int
                        int max_qlen, int max_kv_len, const int32_t* logit_rows, int n_logit_rows, float* logits_out,
                        long long logits_ld, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Mezilix family engine: a decoder whose layers are PARALLEL blocks (one scalar-gain RMS norm feeds the mixer and
+ * the feed-forward, both are added to the stream), whose mixer is latent key/value attention with a sliding
+ * window over a paged cache of [latent | shared rotated key] rows (evaluated in latent space), whose feed-forward
+ * is a softmax-routed mixture of squared-ReLU experts, with a hashed token-pair embedding, token shift on the
+ * mixer input and a learned average over all earlier layer results after every layer.  The reference has no
+ * such model (its stages are vLLM checkpoints, src/serving/real_model_pipeline.py:98-108); the engine sits behind
+ * the same forward contract as asd_engine_forward so that the same step loop, sampler and stage drive it.
+ *
+ * dtype 0: bf16 weights, cache and matrix inputs with fp32 accumulation; dtype 1: everything fp32 (CUDA-core FMA).
+ * In both, norms, rotary angles, scores, softmax, router, residual stream and carried state are fp32.
+ * Every layer has its own sizes.  experts == 0: the layer has no feed-forward.
+ * Carried state besides the cache (caller allocated, zero filled): token ring i32 [max_seqs][ring] and shift ring
+ * fp32 [n_layers][max_seqs][ring][width], both indexed by position % ring (ring >= the longest speculative tail
+ * that may be re-fed).  Cache pool: per layer [num_pages][page_size][kv_rank + rot_dim], layers back to back.
+ */
+typedef struct asd_mezilix_layer_config {
+    int heads, dim, rot_dim, vdim, kv_rank; /* per head: dim unrotated + rot_dim rotated query/key, vdim value */
+    int rot_dims;                           /* rotating coordinates of the rotated part (even, <= rot_dim) */
+    int window;                             /* position p attends p - window < j <= p */
+    float rot_base, scale;
+    int experts, top, ff;
+} asd_mezilix_layer_config;
+typedef struct asd_mezilix_config {
+    int width, vocab, n_layers;
+    float eps;
+    int buckets, mul_prev, mul_cur; /* token-pair table: row (prev * mul_prev + cur * mul_cur) % buckets, row `buckets` first */
+    int max_tokens, page_size, ring, dtype;
+} asd_mezilix_config;
+typedef struct asd_mezilix_engine asd_mezilix_engine_t;
+
+ASD_API asd_mezilix_engine_t* asd_mezilix_create(const asd_mezilix_config* cfg, const asd_mezilix_layer_config* layers);
+ASD_API void asd_mezilix_destroy(asd_mezilix_engine_t* e);
+/* all weights in the engine's dtype, row-major [out, in]; embed [vocab, width], pair_table [buckets + 1, width],
+ * final_gain [1], head [vocab, width] */
+ASD_API int asd_mezilix_set_globals(asd_mezilix_engine_t* e, const void* embed, const void* pair_table,
+                                    const void* final_gain, const void* head);
+/* gain [1]; shift [width]; depth_coeff [layer + 2]; wqd [heads * (dim + rot_dim) + kv_rank + rot_dim, width] = query
+ * rows head by head, then the latent rows, then the rotated key rows; latent_gain [kv_rank]; wuk [heads * dim, kv_rank];
+ * wuv [heads * vdim, kv_rank]; wo [width, heads * vdim]; router [experts, width]; w_up [experts, ff, width];
+ * w_down [experts, width, ff] (NULL when experts == 0) */
+ASD_API int asd_mezilix_set_layer(asd_mezilix_engine_t* e, int layer, const void* gain, const void* shift,
+                                  const void* depth_coeff, const void* wqd, const void* latent_gain, const void* wuk,
+                                  const void* wuv, const void* wo, const void* router, const void* w_up,
+                                  const void* w_down);
+ASD_API size_t asd_mezilix_cache_bytes(const asd_mezilix_engine_t* e, int num_pages);
+ASD_API int asd_mezilix_set_cache(asd_mezilix_engine_t* e, void* pool, int num_pages, const int32_t* page_table,
+                                  int max_seqs, int max_pages_per_seq, int32_t* token_ring, float* shift_ring);
+/* options: "tc_linear" (1, default: bf16 projections whose shape the tcgen05 weight-streaming GEMM accepts run on it;
+ * 0: CUDA-core kernel everywhere), "tc_min_rows" (token count from which the tensor-bound CTA-pair GEMM is used) */
+ASD_API int asd_mezilix_set_option(asd_mezilix_engine_t* e, const char* name, int value);
+/* Same contract as asd_engine_forward (M <= max_tokens).  layer_out (optional, fp32 [n_layers][M][width]) receives
+ * the stream that leaves every layer. */
+ASD_API int asd_mezilix_forward(asd_mezilix_engine_t* e, const int32_t* tokens, const int32_t* positions,
+                                const int32_t* token_slot, int M, const int32_t* cu_q, const int32_t* seq_slot, int nseq,
+                                int max_qlen, int max_kv_len, const int32_t* logit_rows, int n_logit_rows,
+                                float* logits_out, long long logits_ld, float* layer_out, void* stream);
+/* Building blocks on their own (tests): y = x W^T on the CUDA cores, any of bf16 (0) / fp32 (1) per operand */
+ASD_API int asd_linear_simt(const void* x, int x_f32, const void* w, int w_f32, void* y, int y_f32, int M, int N, int K,
+                            void* stream);
+
 #ifdef __cplusplus
 }
 #endif
