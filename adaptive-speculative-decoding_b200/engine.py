@@ -599,6 +599,8 @@ class TPQwenEngine(_BatchOps):
             e.load_hf_weights(w)
         return self
 
+    load_weights = load_hf_weights
+
     def load_random(self, seed: int, std: float = 0.02):
         for e in self.ranks:
             e.load_random(seed, std)

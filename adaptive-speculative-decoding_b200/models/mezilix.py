@@ -19,6 +19,7 @@ import torch
 
 ARCHITECTURE = "Mezilix"
 MIXERS = ("latent_attention",)
+NO_WINDOW = 1 << 30
 
 
 @dataclass(frozen=True)
@@ -82,7 +83,7 @@ class MezilixConfig:
                 kw = dict(experts=int(f["router"]["experts"]), top=int(f["router"]["top"]), ff=int(f["expert"]["ff"]))
             layers.append(MezilixLayer(
                 heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=int(m["rot_dim"]), vdim=int(m["vdim"]),
-                kv_rank=int(m["kv_rank"]), window=int(m["mask"]["size"]), rot_base=float(rot.get("base", 10000.0)),
+                kv_rank=int(m["kv_rank"]), window=_window(m.get("mask")), rot_base=float(rot.get("base", 10000.0)),
                 rot_dims=int(rot.get("dims", m["rot_dim"])), scale=float(m["scale"]), **kw))
         bg = d["embedding"]["bigram"]
         return cls(width=int(d["width"]), vocab_size=int(d["vocab"]), layers=layers, eps=float(d["norm"]["eps"]),
@@ -122,6 +123,12 @@ class MezilixConfig:
 
     def kv_bytes_per_token(self, elem: int = 2) -> int:
         return sum(l.cache_row for l in self.layers) * elem
+
+
+def _window(mask) -> int:
+    """a layer without a mask entry attends to everything before it"""
+    size = (mask or {}).get("size")
+    return NO_WINDOW if size is None else int(size)
 
 
 def tiny_config(**kw) -> MezilixConfig:

@@ -2,8 +2,9 @@
 (src/serving/pipeline.py:14, src/serving/server.py:23,151-164) from ``src/models/stage.py``, a file the
 reference does not ship; the signatures below are reconstructed from those call sites and from the
 listing in docs/guides/RESEARCH_PROTOCOL.md:233-304.  Where the reference's
-Stage wraps ``vllm.LLM`` this one wraps the B200 engine: a ``QwenEngine`` target, optionally
-accelerated by a smaller draft engine through chain draft-then-verify (``SpecDecoder``)."""
+Stage wraps ``vllm.LLM`` this one wraps a B200 engine chosen by the model registry (``QwenEngine`` for the Qwen2
+family, ``MezilixEngine`` for the Mezilix family), optionally accelerated by a smaller draft engine through chain
+draft-then-verify (``SpecDecoder``)."""
 from __future__ import annotations
 
 import logging
@@ -15,6 +16,7 @@ from typing import Dict, List, Optional, Tuple
 import numpy as np
 
 from .._lib import AsdError
+from . import registry
 from .qwen2 import QWEN25, SIZE_ALIASES, Qwen2Config, get_config
 
 logger = logging.getLogger(__name__)
@@ -99,7 +101,7 @@ class StageConfig:
     cost_per_token: Optional[float] = None
     gpu_ids: Optional[List[int]] = None
     max_model_len: Optional[int] = None
-    config: Optional[Qwen2Config] = None      # architecture override (e.g. a layer-truncated shape for tests)
+    config: Optional[object] = None    # architecture override: a Qwen2Config or MezilixConfig (e.g. a small shape for tests)
 
 
 def validate_gpu_assignment(stages) -> None:
@@ -142,7 +144,7 @@ class Stage:
 
     def __init__(self, model_name: str, model_size: str, tensor_parallel_size: int = 1,
                  gpu_memory_utilization: float = 0.8, quantized: bool = False, *,
-                 cost_per_token: Optional[float] = None, config: Optional[Qwen2Config] = None,
+                 cost_per_token: Optional[float] = None, config: Optional[object] = None,
                  draft: Optional["Stage"] = None, k: int = 5, weights: Optional[dict] = None, seed: int = 0,
                  max_batch: int = 16, max_model_len: int = 4096, device=None, gpu_ids: Optional[List[int]] = None,
                  allow_random_weights: bool = True):
@@ -164,10 +166,21 @@ class Stage:
         self.gpu_ids = [int(g) for g in gpu_ids]
         validate_gpu_assignment([(self.model_size, self.tensor_parallel_size, self.gpu_ids)])
         try:
-            self.cfg = config or get_config(self.model_size)
+            if config is not None:
+                self.cfg = config
+            elif registry.has_config(model_name):
+                _, self.cfg = registry.read_config(model_name)       # the checkpoint says what it is
+            else:
+                self.cfg = get_config(self.model_size)
         except KeyError as e:
             raise ModelLoadError(f"unknown model size {model_size!r}") from e
-        if self.cfg.num_key_value_heads % self.tensor_parallel_size or self.cfg.intermediate_size % self.tensor_parallel_size:
+        except ValueError as e:
+            raise ModelLoadError(str(e)) from e
+        self.family = registry.family_of_config(self.cfg)
+        if self.family.name != "qwen2":
+            if self.tensor_parallel_size != 1:
+                raise ModelLoadError(f"the {self.family.name} engine runs on one GPU (tensor_parallel_size 1)")
+        elif self.cfg.num_key_value_heads % self.tensor_parallel_size or self.cfg.intermediate_size % self.tensor_parallel_size:
             raise ModelLoadError(f"{self.model_size}: {self.cfg.num_key_value_heads} KV heads / ffn "
                                  f"{self.cfg.intermediate_size} do not split over {self.tensor_parallel_size} ranks")
         self.cost_per_token = cost_per_token if cost_per_token is not None else COST_PER_TOKEN.get(self.model_size, 1.0)
@@ -187,7 +200,11 @@ class Stage:
                                      f"{torch.cuda.device_count()} CUDA devices are visible")
             from ..engine import QwenEngine, TPQwenEngine
             mt = max(256, max_batch * (k + 1))
-            if self.tensor_parallel_size == 1:
+            if self.family.name == "mezilix":
+                # the carried-state rings must cover the k + 1 positions a verify step may re-feed
+                self.engine = self.family.engine()(self.cfg, max_seqs=max_batch, max_seq_len=max_model_len,
+                                                   max_tokens=mt, device=f"cuda:{self.gpu_ids[0]}", ring=max(8, k + 2))
+            elif self.tensor_parallel_size == 1:
                 self.engine = QwenEngine(self.cfg, max_seqs=max_batch, max_seq_len=max_model_len, max_tokens=mt,
                                          device=f"cuda:{self.gpu_ids[0]}")
             else:
@@ -202,7 +219,7 @@ class Stage:
     def _load_weights(self, weights, seed, allow_random):
         import os
         if weights is not None:
-            self.engine.load_hf_weights(weights)
+            self.engine.load_weights(weights)
             return "state_dict"
         if os.path.isdir(self.model_name):
             from .qwen2 import load_safetensors_dir
@@ -211,7 +228,7 @@ class Stage:
             except FileNotFoundError:
                 w = None
             if w is not None:
-                self.engine.load_hf_weights(w)
+                self.engine.load_weights(w)
                 return "safetensors:" + self.model_name
         if not allow_random:
             raise ModelLoadError(f"no checkpoint found at {self.model_name!r} and random weights are not allowed")
@@ -291,7 +308,8 @@ class Stage:
                 "tensor_parallel_size": self.tensor_parallel_size, "gpu_ids": list(self.gpu_ids),
                 "cost_per_token": self.cost_per_token, "weights": self.weights_source,
                 "dtype": "bfloat16", "hidden_size": self.cfg.hidden_size, "num_layers": self.cfg.num_hidden_layers,
-                "draft": None if self.draft is None else self.draft.model_size, "engine": "asd_b200 (sm_100a)"}
+                "draft": None if self.draft is None else self.draft.model_size, "engine": "asd_b200 (sm_100a)",
+                "family": self.family.name}
 
     def compute_kv_cache_size(self, seq_len: int) -> float:
         """GB of KV cache for one sequence (exact for the Qwen2.5 shape; the reference's listing uses a

@@ -131,7 +131,7 @@ def random_model(cfg: dict, seed: int, scale: float = 1.0) -> Dict[str, torch.Te
     D, V = cfg["width"], cfg["vocab"]
 
     def rn(*shape, std=1.0, mean=0.0):
-        return (torch.randn(*shape, generator=g) * std + mean).to(torch.bfloat16)
+        return (torch.randn(tuple(shape), generator=g) * std + mean).to(torch.bfloat16)
 
     w = {"embed": rn(V, D), "bigram": rn(cfg["embedding"]["bigram"]["buckets"] + 1, D, std=0.5)}
     n = len(cfg["layers"])
