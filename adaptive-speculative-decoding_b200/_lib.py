@@ -99,6 +99,8 @@ def lib() -> ctypes.CDLL:
         "asd_mezilix_set_option": (i32, [vp, c.c_char_p, i32]),
         "asd_mezilix_forward": (i32, [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, vp, i32, vp, c.c_longlong, vp, vp]),
         "asd_linear_simt": (i32, [vp, i32, vp, i32, vp, i32, i32, i32, i32, vp]),
+        "asd_linear_tc": (i32, [vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp]),
+        "asd_mezilix_device_error": (i32, [vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(L, name, None)

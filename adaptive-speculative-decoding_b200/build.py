@@ -23,7 +23,7 @@ FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-li
 COMPONENTS = {
     "core": ["core.cu"],
     "linear": ["gemm.cu"],
-    "mezilix": ["mezilix_engine.cu", "linear_simt.cu", "stream_ops.cu", "latent_attention.cu", "moe.cu"],
+    "mezilix": ["mezilix_engine.cu", "linear_simt.cu", "linear_tc.cu", "stream_ops.cu", "latent_attention.cu", "moe.cu"],
     "qwen": ["engine.cu", "layers.cu", "attention.cu", "attention_tc.cu", "gemm_tc.cu", "forward_persist.cu"],
     "sampling": ["api.cu", "sampler.cu", "stop_rule.cu"],
 }

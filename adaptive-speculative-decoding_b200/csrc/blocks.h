@@ -15,10 +15,10 @@ namespace asd {
 // A row of the result depends on nothing but its own A row, so it is identical however the rows are batched.
 struct SimtLinear {
     const void* a = nullptr;  // element (z, m, k) at a + z * a_zs + row(m) * lda + k
-    const void* w = nullptr;  // w_kn == 0: (z, n, k) at w + z * w_zs + n * ldw + k;  w_kn == 1: at w + z * w_zs + k * ldw + n
+    const void* w = nullptr;  // element (z, n, k) at w + z * w_zs + n * ldw + k
     void* c = nullptr;        // (z, m, n) at c + z * c_zs + m * ldc + n
     long long lda = 0, ldw = 0, ldc = 0, a_zs = 0, w_zs = 0, c_zs = 0;
-    int a_f32 = 0, w_f32 = 0, c_f32 = 1, w_kn = 0;
+    int a_f32 = 0, w_f32 = 0, c_f32 = 1;
     int M = 0, N = 0, K = 0, Z = 1;
     // grouped form (mixture of experts): rows of batch z are [group_off[z], group_off[z + 1]) of A and C (device array,
     // M = upper bound of rows per group, a_zs and c_zs ignored); gather (optional) maps such a row to its row of A
@@ -27,6 +27,13 @@ struct SimtLinear {
     int epilogue = 0;         // 0 none, 1 relu(x)^2
 };
 int launch_simt_linear(const SimtLinear& L, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------- linear_tc.cu
+// The same operation on tcgen05 (bf16 weights; bf16 or fp32 activations, rounded to bf16; fp32 accumulation in TMEM)
+// for shapes it supports: K, ldw and the weight batch stride multiples of 8, 16-byte aligned bases, activation rows
+// 16-byte aligned.  err_flag (device int, may be nullptr) is raised if a bounded wait inside the kernel ran out.
+bool tc_linear_supports(const SimtLinear& L);
+int launch_tc_linear(const SimtLinear& L, int* err_flag, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------------------------- stream_ops.cu
 // Carried per-sequence state: rings of `ring` entries indexed by position % ring, so that a caller that re-feeds the

@@ -53,19 +53,10 @@ __global__ void __launch_bounds__(256) simt_linear_kernel(SimtLinear L) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
             As[lk][lr + 16 * i] = (arow[i] >= 0 && k < L.K) ? ldf(A + arow[i] * L.lda + k) : 0.f;
-        if (!L.w_kn) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int n = n0 + lr + 16 * i;
-                Ws[lk][lr + 16 * i] = (n < L.N && k < L.K) ? ldf(W + (long long)n * L.ldw + k) : 0.f;
-            }
-        } else {  // weights stored [k][n]: n fastest
-            const int ln = tid & 63, lkk = tid >> 6;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int kk = k0 + lkk + 4 * i, n = n0 + ln;
-                Ws[lkk + 4 * i][ln] = (n < L.N && kk < L.K) ? ldf(W + (long long)kk * L.ldw + n) : 0.f;
-            }
+        for (int i = 0; i < 4; ++i) {
+            const int n = n0 + lr + 16 * i;
+            Ws[lk][lr + 16 * i] = (n < L.N && k < L.K) ? ldf(W + (long long)n * L.ldw + k) : 0.f;
         }
         __syncthreads();
 #pragma unroll

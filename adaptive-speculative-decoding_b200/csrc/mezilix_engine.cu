@@ -50,6 +50,7 @@ struct MzEngine : asd_mezilix_engine {
     int *expert_of = nullptr, *counters = nullptr, *group_off = nullptr, *sorted_tok = nullptr, *slot_of = nullptr;
     std::vector<void*> owned;
     int tc_linear = 1;
+    int* dev_error = nullptr;    // raised by a kernel whose bounded wait ran out
     int device = 0;
     struct TcEntry {
         GemmPlan pl;
@@ -92,6 +93,12 @@ static int dense(MzEngine* e, const void* x, const void* w, float* y, int M, int
     return launch_simt_linear(L, s);
 }
 
+// batched / grouped linear: tcgen05 in the bf16 engine when the shape allows, CUDA cores otherwise
+static int linear(MzEngine* e, const SimtLinear& L, cudaStream_t s) {
+    if (!e->f32 && e->tc_linear && tc_linear_supports(L)) return launch_tc_linear(L, e->dev_error, s);
+    return launch_simt_linear(L, s);
+}
+
 static int forward(MzEngine* e, const int* tokens, const int* positions, const int* token_slot, int M, const int* cu_q,
                    const int* seq_slot, int nseq, int max_qlen, const int* logit_rows, int n_rows, float* logits,
                    long long ld, float* layer_out, cudaStream_t s) {
@@ -115,13 +122,13 @@ static int forward(MzEngine* e, const int* tokens, const int* positions, const i
         const LatentDims dm{c.heads, c.dim, c.rot_dim, c.vdim, c.kv_rank, c.rot_dims, c.window, c.scale};
         const PagedRows cache{e->pool + ly.cache_off * e->esz, f32, e->page_table, e->max_pages, e->c.page_size};
         if (launch_latent_post(ix, e->qd, dm, ly.latent_gain, f32, e->c.eps, ly.inv_freq, cache, e->qlat, s)) return -1;
-        {   // q_lat[m][h][0:R] = sum_d q[m][h][d] * Wuk[h * dn + d][:]
+        {   // q_lat[m][h][r] = sum_d q[m][h][d] * WukT[h][r][d]
             SimtLinear L;
             L.a = e->qd, L.a_f32 = 1, L.lda = ly.nqd, L.a_zs = c.dim + c.rot_dim;
-            L.w = ly.wuk, L.w_f32 = f32, L.ldw = c.kv_rank, L.w_zs = (long long)c.dim * c.kv_rank, L.w_kn = 1;
+            L.w = ly.wuk, L.w_f32 = f32, L.ldw = c.dim, L.w_zs = (long long)c.dim * c.kv_rank;
             L.c = e->qlat, L.c_f32 = 1, L.ldc = (long long)c.heads * ly.rw, L.c_zs = ly.rw;
             L.M = M, L.N = c.kv_rank, L.K = c.dim, L.Z = c.heads;
-            if (launch_simt_linear(L, s)) return -1;
+            if (linear(e, L, s)) return -1;
         }
         if (launch_latent_attention(ix, cu_q, seq_slot, nseq, max_qlen, e->qlat, dm, cache, e->olat, s)) return -1;
         {   // v[m][h][:] = Wuv[h] * out_lat[m][h][:]
@@ -130,7 +137,7 @@ static int forward(MzEngine* e, const int* tokens, const int* positions, const i
             L.w = ly.wuv, L.w_f32 = f32, L.ldw = c.kv_rank, L.w_zs = (long long)c.vdim * c.kv_rank;
             L.c = e->vout, L.c_f32 = f32, L.ldc = (long long)c.heads * c.vdim, L.c_zs = c.vdim;
             L.M = M, L.N = c.vdim, L.K = c.kv_rank, L.Z = c.heads;
-            if (launch_simt_linear(L, s)) return -1;
+            if (linear(e, L, s)) return -1;
         }
         if (dense(e, e->vout, ly.wo, e->mix, M, D, c.heads * c.vdim, D, l * 8 + 1, s)) return -1;
         if (c.experts > 0) {
@@ -149,14 +156,14 @@ static int forward(MzEngine* e, const int* tokens, const int* positions, const i
             U.c = e->act, U.c_f32 = f32, U.ldc = c.ff;
             U.M = M, U.N = c.ff, U.K = D, U.Z = c.experts;
             U.group_off = e->group_off, U.gather = e->sorted_tok, U.epilogue = 1;
-            if (launch_simt_linear(U, s)) return -1;
+            if (linear(e, U, s)) return -1;
             SimtLinear W;
             W.a = e->act, W.a_f32 = f32, W.lda = c.ff;
             W.w = ly.w_down, W.w_f32 = f32, W.ldw = c.ff, W.w_zs = (long long)D * c.ff;
             W.c = e->eout, W.c_f32 = 1, W.ldc = D;
             W.M = M, W.N = D, W.K = c.ff, W.Z = c.experts;
             W.group_off = e->group_off;
-            if (launch_simt_linear(W, s)) return -1;
+            if (linear(e, W, s)) return -1;
         }
         LayerClose C;
         C.x_in = l == 0 ? e->stack : e->xavg;
@@ -256,6 +263,8 @@ asd_mezilix_engine_t* asd_mezilix_create(const asd_mezilix_config* cfg, const as
     rc |= dev_alloc(e, &e->group_off, E + 1);
     rc |= dev_alloc(e, &e->sorted_tok, MT * top);
     rc |= dev_alloc(e, &e->slot_of, MT * top);
+    rc |= dev_alloc(e, &e->dev_error, 1);
+    if (!rc && cudaMemset(e->dev_error, 0, sizeof(int)) != cudaSuccess) rc = -1;
     if (rc) {
         asd_mezilix_destroy(e);
         return nullptr;
@@ -351,6 +360,26 @@ int asd_mezilix_forward(asd_mezilix_engine_t* h, const int32_t* tokens, const in
     return forward(e, tokens, positions, token_slot, M, cu_q, seq_slot, nseq, max_qlen, logit_rows,
                    logit_rows ? n_logit_rows : (n_logit_rows > 0 ? M : 0), logits_out, logits_ld, layer_out,
                    static_cast<cudaStream_t>(stream));
+}
+
+int asd_mezilix_device_error(asd_mezilix_engine_t* h) {
+    MzEngine* e = static_cast<MzEngine*>(h);
+    if (!e) return set_error("asd_mezilix_device_error: NULL engine");
+    int v = 0;
+    ASD_CUDA(cudaMemcpy(&v, e->dev_error, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v) return set_error("a Mezilix kernel gave up a bounded wait (tcgen05 linear)");
+    return 0;
+}
+
+int asd_linear_tc(const void* x, int x_f32, const void* w, void* y, int y_f32, int M, int N, int K, int Z,
+                  const int32_t* group_off, const int32_t* gather, int relu_sq, int32_t* err_flag, void* stream) {
+    SimtLinear L;
+    L.a = x, L.a_f32 = x_f32, L.lda = K, L.a_zs = (long long)M * K;
+    L.w = w, L.w_f32 = 0, L.ldw = K, L.w_zs = (long long)N * K;
+    L.c = y, L.c_f32 = y_f32, L.ldc = N, L.c_zs = (long long)M * N;
+    L.M = M, L.N = N, L.K = K, L.Z = Z, L.epilogue = relu_sq ? 1 : 0;
+    L.group_off = group_off, L.gather = gather;
+    return launch_tc_linear(L, err_flag, static_cast<cudaStream_t>(stream));
 }
 
 int asd_linear_simt(const void* x, int x_f32, const void* w, int w_f32, void* y, int y_f32, int M, int N, int K,

@@ -197,8 +197,8 @@ def random_weights(cfg: MezilixConfig, seed: int, device="cpu", dtype=torch.bflo
 
 
 def pack_layer(w: Dict[str, torch.Tensor], cfg: MezilixConfig, i: int, device, dtype) -> Dict[str, Optional[torch.Tensor]]:
-    """checkpoint names -> engine layout of layer i: the query and latent projections stacked into one matrix, the
-    experts stacked into [experts, ff, width] / [experts, width, ff]"""
+    """checkpoint names -> engine layout of layer i: the query and latent projections stacked into one matrix, the key
+    up-projection transposed per head, the experts stacked into [experts, ff, width] / [experts, width, ff]"""
     l, p = cfg.layers[i], f"l{i}."
     dev = lambda t: t.to(device=device, dtype=dtype).contiguous()
     want = tensor_shapes(cfg)
@@ -210,7 +210,9 @@ def pack_layer(w: Dict[str, torch.Tensor], cfg: MezilixConfig, i: int, device, d
                 raise ValueError(f"tensor {k} has shape {tuple(w[k].shape)}, the configuration says {tuple(want[k])}")
     out = {"gain": dev(w[p + "norm1"].reshape(1)), "shift": dev(w[p + "shift"]), "coeff": dev(w[p + "dwa"]),
            "wqd": dev(torch.cat([w[p + "mix.q"], w[p + "mix.dkv"]], 0)), "latent_gain": dev(w[p + "mix.dkv.norm"]),
-           "wuk": dev(w[p + "mix.uk"]), "wuv": dev(w[p + "mix.uv"]), "wo": dev(w[p + "mix.o"]),
+           # per head [kv_rank, dim]: the query is carried into latent space as a product with rows of this matrix
+           "wuk": dev(w[p + "mix.uk"].reshape(l.heads, l.dim, l.kv_rank).transpose(1, 2)),
+           "wuv": dev(w[p + "mix.uv"]), "wo": dev(w[p + "mix.o"]),
            "router": None, "w_up": None, "w_down": None}
     if l.experts:
         out["router"] = dev(w[p + "mlp.router"])

@@ -278,7 +278,8 @@ ASD_API void asd_mezilix_destroy(asd_mezilix_engine_t* e);
 ASD_API int asd_mezilix_set_globals(asd_mezilix_engine_t* e, const void* embed, const void* pair_table,
                                     const void* final_gain, const void* head);
 /* gain [1]; shift [width]; depth_coeff [layer + 2]; wqd [heads * (dim + rot_dim) + kv_rank + rot_dim, width] = query
- * rows head by head, then the latent rows, then the rotated key rows; latent_gain [kv_rank]; wuk [heads * dim, kv_rank];
+ * rows head by head, then the latent rows, then the rotated key rows; latent_gain [kv_rank]; wuk [heads][kv_rank][dim] (the key
+ * up-projection transposed per head);
  * wuv [heads * vdim, kv_rank]; wo [width, heads * vdim]; router [experts, width]; w_up [experts, ff, width];
  * w_down [experts, width, ff] (NULL when experts == 0) */
 ASD_API int asd_mezilix_set_layer(asd_mezilix_engine_t* e, int layer, const void* gain, const void* shift,
@@ -297,7 +298,16 @@ ASD_API int asd_mezilix_forward(asd_mezilix_engine_t* e, const int32_t* tokens, 
                                 const int32_t* token_slot, int M, const int32_t* cu_q, const int32_t* seq_slot, int nseq,
                                 int max_qlen, int max_kv_len, const int32_t* logit_rows, int n_logit_rows,
                                 float* logits_out, long long logits_ld, float* layer_out, void* stream);
-/* Building blocks on their own (tests): y = x W^T on the CUDA cores, any of bf16 (0) / fp32 (1) per operand */
+/* non-zero (and an error message) if a kernel of this engine gave up a bounded wait since creation; synchronises */
+ASD_API int asd_mezilix_device_error(asd_mezilix_engine_t* e);
+/* Building blocks on their own (tests).  asd_linear_tc: y[z] = x[z] w[z]^T on tcgen05 with bf16 weights [Z][N][K], x
+ * bf16 or fp32 [Z][M][K] (rounded to bf16), y bf16 or fp32 [Z][M][N]; K % 8 == 0.  Grouped form (group_off != NULL,
+ * int32 [Z + 1] on the device): rows [group_off[z], group_off[z + 1]) of y come from weight z and from the rows
+ * gather[.] of x (or the same rows if gather == NULL); M bounds the rows of a group.  relu_sq: y = max(y, 0)^2.
+ * err_flag: device int raised if a wait inside the kernel ran out (may be NULL). */
+ASD_API int asd_linear_tc(const void* x, int x_f32, const void* w, void* y, int y_f32, int M, int N, int K, int Z,
+                          const int32_t* group_off, const int32_t* gather, int relu_sq, int32_t* err_flag, void* stream);
+/* y = x W^T on the CUDA cores, any of bf16 (0) / fp32 (1) per operand */
 ASD_API int asd_linear_simt(const void* x, int x_f32, const void* w, int w_f32, void* y, int y_f32, int M, int N, int K,
                             void* stream);
 

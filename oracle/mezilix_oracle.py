@@ -122,7 +122,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], dtype=torc
         x = depth_average(results, w[p + "dwa"])
         leaving.append(x)
     logits = scalar_rms_norm(x, w["final.norm"], eps) @ w["head"].T
-    return logits, torch.stack(leaving)
+    return logits, (torch.stack(leaving) if leaving else x.new_zeros(0, T, x.shape[-1]))
 
 
 def random_model(cfg: dict, seed: int, scale: float = 1.0) -> Dict[str, torch.Tensor]:

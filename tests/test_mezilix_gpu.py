@@ -50,6 +50,13 @@ def make_engine(cfg_dict, w, dtype=torch.float32, max_tokens=64, max_seq_len=512
     return eng
 
 
+def close(eng):
+    """no kernel of the engine gave up a wait"""
+    from asd_b200._lib import check, lib
+    check(lib().asd_mezilix_device_error(eng.h), "device error")
+    eng.close()
+
+
 def tokens(n, vocab, seed):
     return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
 
@@ -212,28 +219,65 @@ def test_pages_and_slots_freed_and_used_again():
 
 
 def standout_model(window, n_layers=1):
-    """one layer, sharp softmax (large scale), weights that make scores spread: single keys carry most of the weight,
-    so a key that is missed just inside the window's edge, or seen just outside it, moves the logits a lot"""
+    """sharp softmax (large scale) and weights that spread the scores: single keys carry most of the weight"""
     cfg = config([layer(heads=2, dim=16, rot_dim=8, vdim=16, kv_rank=32, window=window, scale=3.0, experts=0)
                   for _ in range(n_layers)])
     return cfg, O.random_model(cfg, seed=19, scale=2.0)
 
 
-@pytest.mark.parametrize("window", [9, 16, 33, 300])
-def test_window_edges_with_standout_keys(window):
+def plant_pair(cfg, w, key_tok, query_tok, boost=600.0):
+    """Makes the first layer's queries of ``query_tok`` point at the unrotated keys of ``key_tok`` in every head, so
+    that this one score exceeds all others by about ``boost`` wherever the key is visible.  The pair table and the
+    first layer's shift are silenced, so that what the first layer reads depends on the token alone."""
+    m, eps = cfg["layers"][0]["mixer"], cfg["norm"]["eps"]
+    H, dn, dr, R = m["heads"], m["dim"], m["rot_dim"], m["kv_rank"]
+    w["bigram"] = torch.zeros_like(w["bigram"])
+    w["l0.shift"] = torch.zeros_like(w["l0.shift"])
+    f = lambda t: t.double()
+    hk = O.scalar_rms_norm(f(w["embed"][key_tok]), f(w["l0.norm1"]), eps)
+    hq = O.scalar_rms_norm(f(w["embed"][query_tok]), f(w["l0.norm1"]), eps)
+    c = O.unit_rms(f(w["l0.mix.dkv"])[:R] @ hk, eps) * f(w["l0.mix.dkv.norm"])
+    k = (f(w["l0.mix.uk"]) @ c).reshape(H, dn)
+    q = f(w["l0.mix.q"]).reshape(H, dn + dr, -1).clone()
+    for h in range(H):
+        q[h, :dn] += boost / (m["scale"] * (k[h] @ k[h])) * torch.outer(k[h], hq) / (hq @ hq)
+    w["l0.mix.q"] = q.reshape(H * (dn + dr), -1).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("window,page_size", [(9, 16), (16, 16), (33, 4), (300, 16), (257, 8)])
+def test_window_edges_with_standout_keys(window, page_size):
+    """a key that outweighs everything else sits exactly window - 1 positions back (the last one visible) for one
+    query and exactly window positions back (the first one hidden) for another, in a prompt and while decoding, far
+    away among hundreds of keys and on the first and last row of a page"""
     cfg, w = standout_model(window)
-    ids = tokens(340, 96, 21)
+    V = cfg["vocab"]
+    n = window + 2 * page_size + 56
+    ids = [t % (V - 8) for t in tokens(n, V, 21)]
+    at_in, at_out = [], []
+    # (place of the key, distance to its query): last and first row of a page, and two places inside one
+    for i, (a, gap, where) in enumerate(((2 * page_size - 1, window - 1, at_in), (2 * page_size, window, at_out),
+                                         (2 * page_size + 40, window - 1, at_in), (2 * page_size + 51, window, at_out))):
+        key_tok, query_tok = V - 1 - 2 * i, V - 2 - 2 * i          # every pair has tokens of its own
+        plant_pair(cfg, w, key_tok, query_tok)
+        ids[a], ids[a + gap] = key_tok, query_tok
+        where.append(a + gap)
     ref, _ = O.forward(cfg, w, ids)
-    # the same model with the window one shorter / one longer must be far away: the test can see an off-by-one
-    for wrong in (window - 1, window + 1):
+    # the oracle itself says that these places see an off-by-one: a shorter window loses the key of the first kind,
+    # a longer one gains the key of the second kind
+    for wrong, places in ((window - 1, at_in), (window + 1, at_out)):
         c2 = copy.deepcopy(cfg)
         c2["layers"][0]["mixer"]["mask"]["size"] = wrong
         other, _ = O.forward(c2, w, ids)
-        assert rel_err(other.float(), ref)[1] > 0.05
-    for cuts in ([340], [window - 1, 2, 1, 1, window, 1, 1, 1, 1], [300] + [1] * 40):
-        eng = make_engine(cfg, w, max_tokens=512, page_size=16)
+        for p in places:
+            assert rel_err(other[p:p + 1].float(), ref[p:p + 1])[1] > 0.3
+    first_q = min(at_in + at_out)
+    for cuts in ([n], [first_q - 1, 2, 1, 1, 37, 2, 1, 1], [first_q - 3] + [1] * (n - first_q + 3), [2] * (n // 2)):
+        eng = make_engine(cfg, w, max_tokens=512, page_size=page_size)
         slot = eng.open_sequence()
-        assert rel_err(feed(eng, slot, ids, cuts), ref)[1] < 3e-4
+        got = feed(eng, slot, ids, cuts)
+        assert rel_err(got, ref)[1] < 3e-4
+        for p in at_in + at_out:
+            assert rel_err(got[p:p + 1], ref[p:p + 1])[1] < 3e-4
         eng.close()
 
 
@@ -258,7 +302,7 @@ def test_refeeding_recent_positions_finds_their_state():
     slot = eng.open_sequence()
     eng.reserve(slot, 40)
     eng.forward_ragged([(slot, 0, ids[:20], [])])
-    eng.forward_ragged([(slot, 20, wrong[20:25], [])])             # a rejected tail: 21 .. 24 were wrong
+    eng.forward_ragged([(slot, 20, ids[20:21] + wrong[21:25], [])])  # a rejected tail: 21 .. 24 were wrong
     got = eng.forward_ragged([(slot, 21, ids[21:], list(range(19)))])
     assert rel_err(got, ref[21:])[1] < 2e-4
     eng.close()
@@ -281,7 +325,7 @@ def test_bf16_engine_both_linear_paths(tc):
     cut = feed(eng, slot, ids, [50, 2, 7] + [1] * 31)
     assert rel_err(cut, ref)[0] < 3e-2
     assert rel_err(cut, whole.cpu())[0] < 2e-2        # cutting changes roundings only
-    eng.close()
+    close(eng)
 
 
 def test_linear_on_cuda_cores_matches_fp32_matmul():
@@ -300,6 +344,46 @@ def test_linear_on_cuda_cores_matches_fp32_matmul():
         torch.cuda.synchronize()
         ref = xb.cpu().double() @ wb.cpu().double().T
         assert (y.cpu().double() - ref).abs().max() < 1e-4
+
+
+def test_linear_on_tensor_cores_matches_fp32_matmul():
+    """plain, batched per head, and grouped with gathered rows (the expert layers), with the squared-ReLU epilogue;
+    k loops long enough to reuse every shared-memory stage several times; rows and columns that fill no tile"""
+    from asd_b200._lib import check, lib
+    g = torch.Generator().manual_seed(41)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for M, N, K, Z, x32, y32, relu in ((1, 8, 64, 1, 0, 1, 0), (70, 130, 72, 1, 1, 1, 0), (150, 257, 1024, 1, 0, 0, 1),
+                                       (19, 40, 136, 3, 1, 1, 0), (128, 128, 512, 2, 0, 1, 1)):
+        x, wt = torch.randn(Z, M, K, generator=g), torch.randn(Z, N, K, generator=g) / K ** 0.5
+        xd = x.cuda() if x32 else x.cuda().bfloat16()
+        wd = wt.cuda().bfloat16()
+        y = torch.full((Z, M, N), float("nan"), device="cuda", dtype=torch.float32 if y32 else torch.bfloat16)
+        check(lib().asd_linear_tc(xd.data_ptr(), x32, wd.data_ptr(), y.data_ptr(), y32, M, N, K, Z, None, None, relu,
+                                  err.data_ptr(), None))
+        torch.cuda.synchronize()
+        ref = x.bfloat16().double() @ wd.cpu().double().transpose(1, 2)
+        ref = ref.clamp(min=0) ** 2 if relu else ref
+        tol = 1e-4 if y32 else 2e-2
+        assert (y.cpu().double() - ref).abs().max() < tol * max(1.0, ref.abs().max().item()), (M, N, K, Z)
+    # grouped: 5 weights, groups of unequal size (one empty, one larger than a row tile), rows gathered from x
+    E, T, N, K = 5, 300, 72, 200
+    sizes = [0, 7, 140, 1, 33]
+    x, wt = torch.randn(T, K, generator=g), (torch.randn(E, N, K, generator=g) / K ** 0.5).bfloat16()
+    gather = torch.randint(0, T, (sum(sizes),), generator=g).to(torch.int32)
+    off = torch.tensor([0] + torch.tensor(sizes).cumsum(0).tolist(), dtype=torch.int32)
+    y = torch.full((sum(sizes), N), float("nan"), device="cuda")
+    xd, wd, off_d, gather_d = x.cuda().bfloat16(), wt.cuda(), off.cuda(), gather.cuda()     # alive until the sync
+    check(lib().asd_linear_tc(xd.data_ptr(), 0, wd.data_ptr(), y.data_ptr(), 1, T, N, K, E, off_d.data_ptr(),
+                              gather_d.data_ptr(), 1, err.data_ptr(), None))
+    torch.cuda.synchronize()
+    for e in range(E):
+        rows = gather[off[e]:off[e + 1]].long()
+        if len(rows) == 0:
+            continue
+        ref = (x.bfloat16().double()[rows] @ wt[e].double().T).clamp(min=0) ** 2
+        assert (y[off[e]:off[e + 1]].cpu().double() - ref).abs().max() < 1e-4 * max(1.0, ref.abs().max().item())
+    assert not torch.isnan(y).any()
+    assert int(err.item()) == 0
 
 
 def test_greedy_generation_through_stage_and_scheduler():
