@@ -101,6 +101,7 @@ def lib() -> ctypes.CDLL:
         "asd_linear_simt": (i32, [vp, i32, vp, i32, vp, i32, i32, i32, i32, vp]),
         "asd_linear_tc": (i32, [vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp]),
         "asd_mezilix_device_error": (i32, [vp]),
+        "asd_mezilix_profile_read": (i32, [vp, vp, vp, i32]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(L, name, None)

@@ -22,9 +22,9 @@ FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-li
 # component -> translation units; "core" is part of every library
 COMPONENTS = {
     "core": ["core.cu"],
-    "linear": ["gemm.cu"],
+    "linear": ["gemm.cu", "gemm_tc.cu"],
     "mezilix": ["mezilix_engine.cu", "linear_simt.cu", "linear_tc.cu", "stream_ops.cu", "latent_attention.cu", "moe.cu"],
-    "qwen": ["engine.cu", "layers.cu", "attention.cu", "attention_tc.cu", "gemm_tc.cu", "forward_persist.cu"],
+    "qwen": ["engine.cu", "layers.cu", "attention.cu", "attention_tc.cu", "forward_persist.cu"],
     "sampling": ["api.cu", "sampler.cu", "stop_rule.cu"],
 }
 REQUIRES = {"mezilix": ("linear",), "qwen": ("linear",)}

@@ -104,17 +104,36 @@ struct PagedRows {
 // q_lat[m][head][R .. R + dr) (fp32, row length R + dr).  inv_freq fp32 [rot_dims / 2].
 int launch_latent_post(const SeqIndex& ix, const float* qd, const LatentDims& d, const void* c_norm, int wf32, float eps,
                        const float* inv_freq, const PagedRows& cache, float* q_lat, cudaStream_t stream);
-// out_lat fp32 [M][heads][R].  cu_q / seq_slot as in asd_engine_forward; a sequence's tokens are consecutive positions.
+// Workspace of the register-tiled kernel when it cuts a long key range into shares (few query rows, long context):
+// o [o_elems] floats, ml [2 * rows] floats; (token, head) pairs x shares must fit `rows`.  tiled = 0 forces the
+// one-warp-per-pair kernel, which takes any latent size.
+struct AttnSplit {
+    float* o = nullptr;
+    float* ml = nullptr;
+    long long rows = 0, o_elems = 0;
+    int tiled = 1;
+};
+// out_lat fp32 [M][heads][R].  cu_q / seq_slot as in asd_engine_forward; a sequence's tokens are consecutive positions;
+// max_kv_len bounds position + 1 over the batch.
 int launch_latent_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen,
-                            const float* q_lat, const LatentDims& d, const PagedRows& cache, float* out_lat,
-                            cudaStream_t stream);
+                            int max_kv_len, const float* q_lat, const LatentDims& d, const PagedRows& cache,
+                            float* out_lat, const AttnSplit& ws, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------------------------- moe.cu
 // Router: probs = softmax(logits) over all E experts (fp32); the `top` largest are kept with their probabilities as
 // gates (not renormalised; ties go to the lower index).  Then the (token, choice) pairs are grouped by expert:
 // group_off [E + 1], sorted_tok [M * top] (token of each slot), slot_of [M][top].  counters: int [2 E + 1] scratch.
-int launch_moe_route(const float* logits, int M, int E, int top, int* expert_of, float* gate, int* counters,
-                     int* group_off, int* sorted_tok, int* slot_of, cudaStream_t stream);
+// With `in` the kernel computes the logits itself (fp32, one warp per token): logits = x[M][D] . w[E][D]^T.
+struct MoeRouterInput {
+    const void* x;          // [M][D]
+    int x_f32;
+    const void* w;          // [E][D]
+    int w_f32;
+    int D;
+    float* logits_out;      // optional [M][E]
+};
+int launch_moe_route(const float* logits, const MoeRouterInput* in, int M, int E, int top, int* expert_of, float* gate,
+                     int* counters, int* group_off, int* sorted_tok, int* slot_of, cudaStream_t stream);
 
 int preload_blocks();
 

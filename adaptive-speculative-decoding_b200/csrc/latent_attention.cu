@@ -148,6 +148,261 @@ __global__ void __launch_bounds__(512) latent_attn_kernel(SeqIndex ix, const int
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Register-tiled form for latent sizes that are multiples of 4 and at most 512 (RC = ceil(R / 256) <= 2).
+// One CTA = QT = 4 * RPT query rows (TQ consecutive tokens x HG heads of one sequence) x one share of the key tiles.
+// Per tile of 32 keys (fp32 in shared memory, row stride rw + 4 so that float4 reads of 8 different keys hit 32 banks):
+//   scores   thread (qq, kq) = (t / 16, t % 16): rows {qq, qq + 16} x keys {kq, kq + 16}, float4 steps over R + dr;
+//   softmax  warp w owns rows w * QT / 8 ..: running maximum and sum in registers, weights transposed to [key][row];
+//   update   thread (qg, rg) = (warp / 2, (warp % 2) * 32 + lane): rows qg * RPT .. x latent columns {4 rg + 256 i}:
+//            RPT x 4 RC accumulators fed by one float4 of weights (broadcast) and RC float4 of the key row per key.
+// A long key range is cut into shares (blockIdx.y = sequence * nsplit + share) so that few query rows still fill the
+// GPU; every share writes its unnormalised sum, maximum and weight sum, and latent_combine_kernel merges them.
+template <typename T, int RPT, int RC>
+__global__ void __launch_bounds__(256) latent_attn_tiled(SeqIndex ix, const int* cu_q, const int* seq_slot, int TQ, int HG,
+                                                         int nsplit, const float* q_lat, LatentDims d, PagedRows cache,
+                                                         float* out_lat, float* ws_o, float* ws_ml) {
+    constexpr int QT = 4 * RPT, KT = 32, NQ = QT / 16, RW = QT / 8;
+    extern __shared__ float smem[];
+    const int rw = d.R + d.dr, LD = rw + 4;
+    float* Ks = smem;                        // [KT][LD]
+    float* Qs = Ks + KT * LD;                // [QT][LD]
+    float* Ss = Qs + QT * LD;                // [QT][KT + 1]
+    float* Pt = Ss + QT * (KT + 1);          // [KT][QT]
+    float* Cs = Pt + KT * QT;                // [QT] rescale of this tile, then the final weight sums
+    float* Ms = Cs + QT;                     // [QT] final maxima
+    __shared__ int row_pos[32];
+    const int seq = blockIdx.y / nsplit, split = blockIdx.y % nsplit;
+    const int t0 = cu_q[seq] + blockIdx.x * TQ, t_end = cu_q[seq + 1];
+    if (t0 >= t_end) return;
+    const int slot = seq_slot[seq];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_tok = min(TQ, t_end - t0), h0 = blockIdx.z * HG;
+    const int p_first = ix.positions[t0], p_last = ix.positions[t0 + n_tok - 1];
+    int j_lo = p_first - d.window + 1;
+    if (j_lo < 0) j_lo = 0;
+    const int nt = (p_last - j_lo) / KT + 1, per = (nt + nsplit - 1) / nsplit;
+    const int ts = split * per, te = min(nt, ts + per);
+    // row r of the tile = (token t0 + r / HG, head h0 + r % HG)
+    if (tid < QT) {
+        const int tq = tid / HG, h = h0 + tid % HG;
+        row_pos[tid] = (tq < n_tok && h < d.heads && tid < TQ * HG) ? ix.positions[t0 + tq] : -1;
+    }
+    for (int i = tid; i < QT * (rw / 4); i += 256) {
+        const int r = i / (rw / 4), c = i % (rw / 4);
+        const int tq = r / HG, h = h0 + r % HG;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (tq < n_tok && h < d.heads && r < TQ * HG)
+            v = *reinterpret_cast<const float4*>(q_lat + ((long long)(t0 + tq) * d.heads + h) * rw + 4 * c);
+        *reinterpret_cast<float4*>(Qs + r * LD + 4 * c) = v;
+    }
+    float4 acc[RPT][RC];
+#pragma unroll
+    for (int i = 0; i < RPT; ++i)
+#pragma unroll
+        for (int j = 0; j < RC; ++j) acc[i][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float m_run[RW], l_run[RW];
+#pragma unroll
+    for (int i = 0; i < RW; ++i) m_run[i] = -INFINITY, l_run[i] = 0.f;
+    const int kq = tid & 15, qq = tid >> 4;
+    const int qg = warp >> 1, rg = (warp & 1) * 32 + lane;
+    const T* pool = (const T*)cache.pool;
+    for (int t = ts; t < te; ++t) {
+        const int j0 = j_lo + t * KT;
+        __syncthreads();                     // the previous tile is consumed; Qs and row_pos are written
+        for (int r = warp; r < KT; r += 8) {
+            const int kp = j0 + r;
+            if (kp <= p_last) {
+                const T* src = pool + cache_row(cache, slot, kp) * rw;
+                for (int i = lane; i < rw; i += 32) Ks[r * LD + i] = ldf(src + i);
+            } else {
+                for (int i = lane; i < rw; i += 32) Ks[r * LD + i] = 0.f;
+            }
+        }
+        __syncthreads();
+        {   // scores
+            float s[NQ][2];
+#pragma unroll
+            for (int a = 0; a < NQ; ++a) s[a][0] = s[a][1] = 0.f;
+            const float* k0 = Ks + kq * LD;
+            const float* k1 = Ks + (kq + 16) * LD;
+            for (int i = 0; i < rw; i += 4) {
+                const float4 ka = *reinterpret_cast<const float4*>(k0 + i), kb = *reinterpret_cast<const float4*>(k1 + i);
+#pragma unroll
+                for (int a = 0; a < NQ; ++a) {
+                    const float4 q = *reinterpret_cast<const float4*>(Qs + (qq + 16 * a) * LD + i);
+                    s[a][0] = fmaf(q.x, ka.x, s[a][0]), s[a][0] = fmaf(q.y, ka.y, s[a][0]);
+                    s[a][0] = fmaf(q.z, ka.z, s[a][0]), s[a][0] = fmaf(q.w, ka.w, s[a][0]);
+                    s[a][1] = fmaf(q.x, kb.x, s[a][1]), s[a][1] = fmaf(q.y, kb.y, s[a][1]);
+                    s[a][1] = fmaf(q.z, kb.z, s[a][1]), s[a][1] = fmaf(q.w, kb.w, s[a][1]);
+                }
+            }
+#pragma unroll
+            for (int a = 0; a < NQ; ++a) {
+                const int r = qq + 16 * a, p = row_pos[r];
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    const int kp = j0 + kq + 16 * b;
+                    const bool seen = p >= 0 && kp <= p && p - kp < d.window;
+                    Ss[r * (KT + 1) + kq + 16 * b] = seen ? s[a][b] * d.scale : -INFINITY;
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < RW; ++i) {       // softmax bookkeeping of this warp's rows
+            const int r = warp * RW + i;
+            const float sv = Ss[r * (KT + 1) + lane];
+            const float m_new = fmaxf(m_run[i], warp_max(sv));
+            float corr = 1.f, w = 0.f;
+            if (m_new != -INFINITY) {
+                corr = expf(m_run[i] - m_new);      // exp(-inf) = 0 on the row's first visible tile
+                w = sv == -INFINITY ? 0.f : expf(sv - m_new);
+            }
+            l_run[i] = l_run[i] * corr + warp_sum(w);
+            m_run[i] = m_new;
+            Pt[lane * QT + r] = w;
+            if (lane == 0) Cs[r] = corr;
+        }
+        __syncthreads();
+        {   // update
+            float cr[RPT];
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) cr[i] = Cs[qg * RPT + i];
+#pragma unroll
+            for (int i = 0; i < RPT; ++i)
+#pragma unroll
+                for (int j = 0; j < RC; ++j)
+                    acc[i][j].x *= cr[i], acc[i][j].y *= cr[i], acc[i][j].z *= cr[i], acc[i][j].w *= cr[i];
+            for (int k = 0; k < KT; ++k) {
+                float w[RPT];
+#pragma unroll
+                for (int i = 0; i < RPT; i += 4) {
+                    const float4 v = *reinterpret_cast<const float4*>(Pt + k * QT + qg * RPT + i);
+                    w[i] = v.x, w[i + 1] = v.y, w[i + 2] = v.z, w[i + 3] = v.w;
+                }
+#pragma unroll
+                for (int j = 0; j < RC; ++j) {
+                    const int c = 4 * rg + 256 * j;
+                    if (c < d.R) {
+                        const float4 kv = *reinterpret_cast<const float4*>(Ks + k * LD + c);
+#pragma unroll
+                        for (int i = 0; i < RPT; ++i) {
+                            acc[i][j].x = fmaf(w[i], kv.x, acc[i][j].x), acc[i][j].y = fmaf(w[i], kv.y, acc[i][j].y);
+                            acc[i][j].z = fmaf(w[i], kv.z, acc[i][j].z), acc[i][j].w = fmaf(w[i], kv.w, acc[i][j].w);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < RW; ++i) Cs[warp * RW + i] = l_run[i], Ms[warp * RW + i] = m_run[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+        const int r = qg * RPT + i;
+        if (row_pos[r] < 0) continue;
+        const int tq = r / HG, h = h0 + r % HG;
+        const long long row = (long long)(t0 + tq) * d.heads + h;
+        if (nsplit == 1) {
+            const float inv = 1.f / Cs[r];
+#pragma unroll
+            for (int j = 0; j < RC; ++j) {
+                const int c = 4 * rg + 256 * j;
+                if (c < d.R)
+                    *reinterpret_cast<float4*>(out_lat + row * d.R + c) =
+                        make_float4(acc[i][j].x * inv, acc[i][j].y * inv, acc[i][j].z * inv, acc[i][j].w * inv);
+            }
+        } else {
+            const long long part = row * nsplit + split;
+#pragma unroll
+            for (int j = 0; j < RC; ++j) {
+                const int c = 4 * rg + 256 * j;
+                if (c < d.R) *reinterpret_cast<float4*>(ws_o + part * d.R + c) = acc[i][j];
+            }
+            if (rg == 0) ws_ml[part * 2] = Ms[r], ws_ml[part * 2 + 1] = Cs[r];
+        }
+    }
+}
+
+// out[row] = sum_s o_s exp(m_s - m) / sum_s l_s exp(m_s - m) over the shares of one (token, head)
+__global__ void latent_combine_kernel(const float* ws_o, const float* ws_ml, int nsplit, int R, float* out_lat) {
+    const long long row = blockIdx.x;
+    float m = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) m = fmaxf(m, ws_ml[(row * nsplit + s) * 2]);
+    float l = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float ms = ws_ml[(row * nsplit + s) * 2];
+        if (ms != -INFINITY) l += ws_ml[(row * nsplit + s) * 2 + 1] * expf(ms - m);
+    }
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            const float ms = ws_ml[(row * nsplit + s) * 2];
+            if (ms != -INFINITY) o += ws_o[(row * nsplit + s) * R + c] * expf(ms - m);
+        }
+        out_lat[row * R + c] = o / l;
+    }
+}
+
+template <typename T, int RPT, int RC>
+int launch_tiled_t(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, int max_kv_len,
+                   const float* q_lat, const LatentDims& d, const PagedRows& cache, float* out_lat, const AttnSplit& ws,
+                   cudaStream_t stream) {
+    constexpr int QT = 4 * RPT;
+    const int HG = d.heads < QT ? d.heads : QT;
+    int TQ = QT / HG;
+    if (TQ > max_qlen) TQ = max_qlen;
+    const int rw = d.R + d.dr, LD = rw + 4;
+    const size_t smem = (size_t)(32 * LD + QT * LD + QT * 33 + 32 * QT + 2 * QT) * sizeof(float);
+    const int q_tiles = (max_qlen + TQ - 1) / TQ, hgs = (d.heads + HG - 1) / HG;
+    // shares of the key range: enough CTAs for two per SM, at least four key tiles each, within the workspace
+    long long keys = (long long)(d.window < max_kv_len ? d.window : max_kv_len) + TQ;
+    const int kv_tiles = (int)((keys + 31) / 32);
+    int nsplit = 1;
+    const long long ctas = (long long)q_tiles * nseq * hgs, rows = (long long)ix.M * d.heads;
+    if (ws.o && ws.ml && ctas < 296) {
+        nsplit = (int)((296 + ctas - 1) / ctas);
+        if (nsplit > kv_tiles / 4) nsplit = kv_tiles / 4;
+        if ((long long)nsplit * rows > ws.rows) nsplit = (int)(ws.rows / rows);
+        if ((long long)nsplit * rows * d.R > ws.o_elems) nsplit = (int)(ws.o_elems / (rows * d.R));
+        if (nsplit < 1) nsplit = 1;
+        if (nsplit > 64) nsplit = 64;
+    }
+    auto fn = latent_attn_tiled<T, RPT, RC>;
+    ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(q_tiles, nseq * nsplit, hgs);
+    fn<<<grid, 256, smem, stream>>>(ix, cu_q, seq_slot, TQ, HG, nsplit, q_lat, d, cache, out_lat, ws.o, ws.ml);
+    count_launch(1);
+    if (nsplit > 1) {
+        latent_combine_kernel<<<(unsigned)rows, 128, 0, stream>>>(ws.o, ws.ml, nsplit, d.R, out_lat);
+        count_launch(1);
+    }
+    ASD_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <typename T>
+int launch_tiled(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, int max_kv_len,
+                 const float* q_lat, const LatentDims& d, const PagedRows& cache, float* out_lat, const AttnSplit& ws,
+                 cudaStream_t stream) {
+    const long long need = (long long)(d.heads < 32 ? d.heads : 32) * (max_qlen < 32 ? max_qlen : 32);
+    const bool small = need <= 16;
+#define ASD_TILED(RPT, RC) \
+    return launch_tiled_t<T, RPT, RC>(ix, cu_q, seq_slot, nseq, max_qlen, max_kv_len, q_lat, d, cache, out_lat, ws, stream)
+    if (d.R <= 256) {
+        if (small) ASD_TILED(4, 1);
+        ASD_TILED(8, 1);
+    }
+    if (small) ASD_TILED(4, 2);
+    ASD_TILED(8, 2);
+#undef ASD_TILED
+}
+
 template <typename T>
 int launch_attn_t(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, const float* q_lat,
                   const LatentDims& d, const PagedRows& cache, float* out_lat, cudaStream_t stream) {
@@ -196,10 +451,17 @@ int launch_latent_post(const SeqIndex& ix, const float* qd, const LatentDims& d,
 }
 
 int launch_latent_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen,
-                            const float* q_lat, const LatentDims& d, const PagedRows& cache, float* out_lat,
-                            cudaStream_t stream) {
+                            int max_kv_len, const float* q_lat, const LatentDims& d, const PagedRows& cache,
+                            float* out_lat, const AttnSplit& ws, cudaStream_t stream) {
     if (ix.M <= 0 || nseq <= 0) return 0;
     if (d.window <= 0) return set_error("latent attention: window must be positive");
+    const int rw = d.R + d.dr;
+    const bool tiled = ws.tiled && (d.R % 4) == 0 && (rw % 4) == 0 && d.R <= 512 &&
+                       (size_t)(64 * (rw + 4)) * sizeof(float) <= 200 * 1024 &&
+                       (reinterpret_cast<uintptr_t>(q_lat) & 15) == 0 && (reinterpret_cast<uintptr_t>(out_lat) & 15) == 0;
+    if (tiled)
+        return cache.f32 ? launch_tiled<float>(ix, cu_q, seq_slot, nseq, max_qlen, max_kv_len, q_lat, d, cache, out_lat, ws, stream)
+                         : launch_tiled<__nv_bfloat16>(ix, cu_q, seq_slot, nseq, max_qlen, max_kv_len, q_lat, d, cache, out_lat, ws, stream);
     return cache.f32 ? launch_attn_t<float>(ix, cu_q, seq_slot, nseq, max_qlen, q_lat, d, cache, out_lat, stream)
                      : launch_attn_t<__nv_bfloat16>(ix, cu_q, seq_slot, nseq, max_qlen, q_lat, d, cache, out_lat, stream);
 }

@@ -18,6 +18,7 @@
 #include "asd_internal.h"
 #include "blocks.h"
 #include "gemm.h"
+#include "prof.h"
 
 struct asd_mezilix_engine {};
 
@@ -50,10 +51,14 @@ struct MzEngine : asd_mezilix_engine {
     int *expert_of = nullptr, *counters = nullptr, *group_off = nullptr, *sorted_tok = nullptr, *slot_of = nullptr;
     std::vector<void*> owned;
     int tc_linear = 1;
+    int tc_min_rows = 257;       // token count from which dense projections use the tensor-bound CTA-pair GEMM
+    EventProfiler prof;
+    AttnSplit attn_ws;           // partial sums of the attention kernel's key-range shares
     int* dev_error = nullptr;    // raised by a kernel whose bounded wait ran out
     int device = 0;
     struct TcEntry {
         GemmPlan pl;
+        TcPlan big;
         CUtensorMap tw, tx;
     };
     std::unordered_map<unsigned long long, TcEntry> tc_cache;
@@ -78,11 +83,18 @@ static int dense(MzEngine* e, const void* x, const void* w, float* y, int M, int
         auto it = e->tc_cache.find(k);
         if (it == e->tc_cache.end()) {
             MzEngine::TcEntry t;
-            if (gemm_plan(&t.pl, M, N, K, GEMM_OUT_F32, 0, 0, 1)) return -1;
             if (make_tmap_bf16(&t.tw, w, N, K, K, 128)) return -1;
-            if (make_tmap_bf16(&t.tx, x, M, K, K, t.pl.MT)) return -1;
+            if (M >= e->tc_min_rows) {   // above the HBM / tensor ridge: 256 weight rows x MT tokens on a CTA pair
+                if (gemm_tc_plan(&t.big, M, N, K, GEMM_OUT_F32, 1, 0)) return -1;
+                if (make_tmap_bf16(&t.tx, x, M, K, K, t.big.MT / 2)) return -1;
+            } else {
+                if (gemm_plan(&t.pl, M, N, K, GEMM_OUT_F32, 0, 0, 1)) return -1;
+                if (make_tmap_bf16(&t.tx, x, M, K, K, t.pl.MT)) return -1;
+            }
             it = e->tc_cache.emplace(k, t).first;
         }
+        if (M >= e->tc_min_rows)
+            return gemm_tc_launch(it->second.big, it->second.tw, it->second.tx, y, ldc, N, 0, false, s, false, nullptr);
         return gemm_launch(it->second.pl, it->second.tw, it->second.tx, y, ldc, N, false, s, false);
     }
     SimtLinear L;
@@ -93,6 +105,9 @@ static int dense(MzEngine* e, const void* x, const void* w, float* y, int M, int
     return launch_simt_linear(L, s);
 }
 
+enum MzProf { MZ_DENSE = 0, MZ_HEADS = 1, MZ_ATTN = 2, MZ_EXPERTS = 3, MZ_ROUTER = 4, MZ_GLUE = 5, MZ_HEAD = 6, MZ_NCLASS = 7 };
+#define MZ_PROF(cls) ProfRegion _region(e->prof, cls, s)
+
 // batched / grouped linear: tcgen05 in the bf16 engine when the shape allows, CUDA cores otherwise
 static int linear(MzEngine* e, const SimtLinear& L, cudaStream_t s) {
     if (!e->f32 && e->tc_linear && tc_linear_supports(L)) return launch_tc_linear(L, e->dev_error, s);
@@ -100,29 +115,41 @@ static int linear(MzEngine* e, const SimtLinear& L, cudaStream_t s) {
 }
 
 static int forward(MzEngine* e, const int* tokens, const int* positions, const int* token_slot, int M, const int* cu_q,
-                   const int* seq_slot, int nseq, int max_qlen, const int* logit_rows, int n_rows, float* logits,
-                   long long ld, float* layer_out, cudaStream_t s) {
+                   const int* seq_slot, int nseq, int max_qlen, int max_kv_len, const int* logit_rows, int n_rows,
+                   float* logits, long long ld, float* layer_out, cudaStream_t s) {
     const int D = e->c.width, ring = e->c.ring, f32 = e->f32;
     const SeqIndex ix{tokens, positions, token_slot, M};
     const size_t stride = (size_t)e->c.max_tokens * D;
     const int nl = e->c.n_layers;
     const void* first_gain = nl ? e->layers[0].gain : e->final_gain;
-    if (launch_embed_pair(ix, e->embed, e->pair_table, f32, e->c.buckets, e->c.mul_prev, e->c.mul_cur, e->tok_ring, ring,
-                          e->stack, first_gain, e->c.eps, e->hn, D, s))
-        return -1;
-    if (launch_commit_tokens(ix, e->tok_ring, ring, s)) return -1;
+    {
+        MZ_PROF(MZ_GLUE);
+        if (launch_embed_pair(ix, e->embed, e->pair_table, f32, e->c.buckets, e->c.mul_prev, e->c.mul_cur, e->tok_ring,
+                              ring, e->stack, first_gain, e->c.eps, e->hn, D, s))
+            return -1;
+        if (launch_commit_tokens(ix, e->tok_ring, ring, s)) return -1;
+    }
     for (int l = 0; l < nl; ++l) {
         MzLayer& ly = e->layers[l];
         const asd_mezilix_layer_config& c = ly.c;
         float* ring_l = e->shift_ring + (size_t)l * e->max_seqs * ring * D;
-        if (launch_token_shift(ix, e->hn, ring_l, ring, ly.shift, f32, e->h, e->hs, f32, D, s)) return -1;
-        if (launch_commit_shift_state(ix, e->hn, ring_l, ring, D, s)) return -1;
-        // queries | latent | rotated key in one projection
-        if (dense(e, e->hs, ly.wqd, e->qd, M, ly.nqd, D, ly.nqd, l * 8 + 0, s)) return -1;
+        {
+            MZ_PROF(MZ_GLUE);
+            if (launch_token_shift(ix, e->hn, ring_l, ring, ly.shift, f32, e->h, e->hs, f32, D, s)) return -1;
+            if (launch_commit_shift_state(ix, e->hn, ring_l, ring, D, s)) return -1;
+        }
+        {   // queries | latent | rotated key in one projection
+            MZ_PROF(MZ_DENSE);
+            if (dense(e, e->hs, ly.wqd, e->qd, M, ly.nqd, D, ly.nqd, l * 8 + 0, s)) return -1;
+        }
         const LatentDims dm{c.heads, c.dim, c.rot_dim, c.vdim, c.kv_rank, c.rot_dims, c.window, c.scale};
         const PagedRows cache{e->pool + ly.cache_off * e->esz, f32, e->page_table, e->max_pages, e->c.page_size};
-        if (launch_latent_post(ix, e->qd, dm, ly.latent_gain, f32, e->c.eps, ly.inv_freq, cache, e->qlat, s)) return -1;
+        {
+            MZ_PROF(MZ_GLUE);
+            if (launch_latent_post(ix, e->qd, dm, ly.latent_gain, f32, e->c.eps, ly.inv_freq, cache, e->qlat, s)) return -1;
+        }
         {   // q_lat[m][h][r] = sum_d q[m][h][d] * WukT[h][r][d]
+            MZ_PROF(MZ_HEADS);
             SimtLinear L;
             L.a = e->qd, L.a_f32 = 1, L.lda = ly.nqd, L.a_zs = c.dim + c.rot_dim;
             L.w = ly.wuk, L.w_f32 = f32, L.ldw = c.dim, L.w_zs = (long long)c.dim * c.kv_rank;
@@ -130,8 +157,14 @@ static int forward(MzEngine* e, const int* tokens, const int* positions, const i
             L.M = M, L.N = c.kv_rank, L.K = c.dim, L.Z = c.heads;
             if (linear(e, L, s)) return -1;
         }
-        if (launch_latent_attention(ix, cu_q, seq_slot, nseq, max_qlen, e->qlat, dm, cache, e->olat, s)) return -1;
+        {
+            MZ_PROF(MZ_ATTN);
+            if (launch_latent_attention(ix, cu_q, seq_slot, nseq, max_qlen, max_kv_len, e->qlat, dm, cache, e->olat,
+                                        e->attn_ws, s))
+                return -1;
+        }
         {   // v[m][h][:] = Wuv[h] * out_lat[m][h][:]
+            MZ_PROF(MZ_HEADS);
             SimtLinear L;
             L.a = e->olat, L.a_f32 = 1, L.lda = (long long)c.heads * c.kv_rank, L.a_zs = c.kv_rank;
             L.w = ly.wuv, L.w_f32 = f32, L.ldw = c.kv_rank, L.w_zs = (long long)c.vdim * c.kv_rank;
@@ -139,17 +172,19 @@ static int forward(MzEngine* e, const int* tokens, const int* positions, const i
             L.M = M, L.N = c.vdim, L.K = c.kv_rank, L.Z = c.heads;
             if (linear(e, L, s)) return -1;
         }
-        if (dense(e, e->vout, ly.wo, e->mix, M, D, c.heads * c.vdim, D, l * 8 + 1, s)) return -1;
+        {
+            MZ_PROF(MZ_DENSE);
+            if (dense(e, e->vout, ly.wo, e->mix, M, D, c.heads * c.vdim, D, l * 8 + 1, s)) return -1;
+        }
         if (c.experts > 0) {
-            SimtLinear R;   // router logits in fp32 on the CUDA cores in both modes
-            R.a = e->h, R.a_f32 = f32, R.lda = D;
-            R.w = ly.router, R.w_f32 = f32, R.ldw = D;
-            R.c = e->rlog, R.c_f32 = 1, R.ldc = c.experts;
-            R.M = M, R.N = c.experts, R.K = D;
-            if (launch_simt_linear(R, s)) return -1;
-            if (launch_moe_route(e->rlog, M, c.experts, c.top, e->expert_of, e->gate, e->counters, e->group_off,
-                                 e->sorted_tok, e->slot_of, s))
-                return -1;
+            {   // router logits in fp32 on the CUDA cores in both modes, fused with the softmax and the choice
+                MZ_PROF(MZ_ROUTER);
+                const MoeRouterInput in{e->h, f32, ly.router, f32, D, nullptr};
+                if (launch_moe_route(nullptr, &in, M, c.experts, c.top, e->expert_of, e->gate, e->counters, e->group_off,
+                                     e->sorted_tok, e->slot_of, s))
+                    return -1;
+            }
+            MZ_PROF(MZ_EXPERTS);
             SimtLinear U;
             U.a = e->h, U.a_f32 = f32, U.lda = D;
             U.w = ly.w_up, U.w_f32 = f32, U.ldw = D, U.w_zs = (long long)c.ff * D;
@@ -165,6 +200,7 @@ static int forward(MzEngine* e, const int* tokens, const int* positions, const i
             W.group_off = e->group_off;
             if (linear(e, W, s)) return -1;
         }
+        MZ_PROF(MZ_GLUE);
         LayerClose C;
         C.x_in = l == 0 ? e->stack : e->xavg;
         C.mix = e->mix;
@@ -180,6 +216,7 @@ static int forward(MzEngine* e, const int* tokens, const int* positions, const i
                                      cudaMemcpyDeviceToDevice, s));
     }
     if (n_rows > 0) {
+        MZ_PROF(MZ_HEAD);
         if (launch_select_rows(e->hn, logit_rows, e->xsel, f32, n_rows, D, s)) return -1;
         const int V = e->c.vocab;
         if (dense(e, e->xsel, e->head, logits, n_rows, V, D, ld ? (int)ld : V, nl * 8 + 2, s)) return -1;
@@ -263,6 +300,10 @@ asd_mezilix_engine_t* asd_mezilix_create(const asd_mezilix_config* cfg, const as
     rc |= dev_alloc(e, &e->group_off, E + 1);
     rc |= dev_alloc(e, &e->sorted_tok, MT * top);
     rc |= dev_alloc(e, &e->slot_of, MT * top);
+    e->attn_ws.rows = 16384;
+    e->attn_ws.o_elems = e->attn_ws.rows * 512;
+    rc |= dev_alloc(e, &e->attn_ws.o, (size_t)e->attn_ws.o_elems);
+    rc |= dev_alloc(e, &e->attn_ws.ml, (size_t)e->attn_ws.rows * 2);
     rc |= dev_alloc(e, &e->dev_error, 1);
     if (!rc && cudaMemset(e->dev_error, 0, sizeof(int)) != cudaSuccess) rc = -1;
     if (rc) {
@@ -335,6 +376,20 @@ int asd_mezilix_set_option(asd_mezilix_engine_t* h, const char* name, int value)
         e->tc_linear = value;
         return 0;
     }
+    if (!strcmp(name, "tc_min_rows")) {
+        e->tc_min_rows = value > 0 ? value : 1 << 30;
+        e->tc_cache.clear();
+        return 0;
+    }
+    if (!strcmp(name, "attn_tiled")) {
+        e->attn_ws.tiled = value;
+        return 0;
+    }
+    if (!strcmp(name, "profile")) {
+        e->prof.on = value;
+        e->prof.reset();
+        return 0;
+    }
     return set_error("asd_mezilix_set_option: unknown option %s", name);
 }
 
@@ -357,9 +412,16 @@ int asd_mezilix_forward(asd_mezilix_engine_t* h, const int32_t* tokens, const in
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev != e->device) return set_error("asd_mezilix_forward: called on device %d, engine lives on %d", dev, e->device);
-    return forward(e, tokens, positions, token_slot, M, cu_q, seq_slot, nseq, max_qlen, logit_rows,
+    return forward(e, tokens, positions, token_slot, M, cu_q, seq_slot, nseq, max_qlen, max_kv_len, logit_rows,
                    logit_rows ? n_logit_rows : (n_logit_rows > 0 ? M : 0), logits_out, logits_ld, layer_out,
                    static_cast<cudaStream_t>(stream));
+}
+
+int asd_mezilix_profile_read(asd_mezilix_engine_t* h, float* ms_by_class, int* launches_by_class, int nclass) {
+    MzEngine* e = static_cast<MzEngine*>(h);
+    if (!e || !ms_by_class || nclass < MZ_NCLASS) return set_error("asd_mezilix_profile_read: bad argument");
+    ASD_CUDA(e->prof.read(ms_by_class, launches_by_class, nclass));
+    return 0;
 }
 
 int asd_mezilix_device_error(asd_mezilix_engine_t* h) {

@@ -13,14 +13,41 @@ namespace asd {
 
 namespace {
 
-// one warp per token; probs of the token live in shared memory (E floats per warp)
-__global__ void moe_route_kernel(const float* logits, int M, int E, int top, int* expert_of, float* gate, int* counts) {
+// one warp per token; probs of the token live in shared memory (E floats per warp).  With x != nullptr the warp first
+// computes the token's router logits itself, z[e] = sum_d x[m][d] * wr[e][d] in fp32 (lane-strided partial sums in
+// increasing d, then the fixed warp tree: the same for a token whatever else is in the batch), eight experts per pass
+// over the row.
+__global__ void moe_route_kernel(const float* logits, const void* x, int xf32, const void* wr, int wf32, int D, float* z_out,
+                                 int M, int E, int top, int* expert_of, float* gate, int* counts) {
     extern __shared__ float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m = blockIdx.x * (blockDim.x >> 5) + warp;
     if (m >= M) return;
     float* pr = sm + (size_t)warp * E;
-    const float* z = logits + (long long)m * E;
+    float* zs = sm + (size_t)(blockDim.x >> 5) * E + (size_t)warp * E;
+    if (x) {
+        for (int e0 = 0; e0 < E; e0 += 8) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            for (int d = lane; d < D; d += 32) {
+                const float xv = ldx(x, (long long)m * D + d, xf32);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (e0 + j < E) acc[j] = fmaf(xv, ldx(wr, (long long)(e0 + j) * D + d, wf32), acc[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float v = warp_sum(acc[j]);
+                if (lane == 0 && e0 + j < E) {
+                    zs[e0 + j] = v;
+                    if (z_out) z_out[(long long)m * E + e0 + j] = v;
+                }
+            }
+        }
+        __syncwarp();
+    }
+    const float* z = x ? zs : logits + (long long)m * E;
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
     mx = warp_max(mx);
@@ -86,14 +113,16 @@ __global__ void moe_scatter_kernel(const int* expert_of, int n, int top, int E, 
 
 }  // namespace
 
-int launch_moe_route(const float* logits, int M, int E, int top, int* expert_of, float* gate, int* counters,
-                     int* group_off, int* sorted_tok, int* slot_of, cudaStream_t stream) {
+int launch_moe_route(const float* logits, const MoeRouterInput* in, int M, int E, int top, int* expert_of, float* gate,
+                     int* counters, int* group_off, int* sorted_tok, int* slot_of, cudaStream_t stream) {
     if (M <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E) return set_error("moe: need 0 < top <= experts (top %d, experts %d)", top, E);
-    if ((size_t)E * 4 * sizeof(float) > 48 * 1024) return set_error("moe: more than 3072 experts");
+    if ((size_t)E * 8 * sizeof(float) > 48 * 1024) return set_error("moe: more than 1536 experts");
+    if (!logits && !in) return set_error("moe: neither logits nor router inputs");
     ASD_CUDA(cudaMemsetAsync(counters, 0, sizeof(int) * E, stream));
-    moe_route_kernel<<<(M + 3) / 4, 128, (size_t)E * 4 * sizeof(float), stream>>>(logits, M, E, top, expert_of, gate,
-                                                                                 counters);
+    moe_route_kernel<<<(M + 3) / 4, 128, (size_t)E * 8 * sizeof(float), stream>>>(
+        logits, in ? in->x : nullptr, in ? in->x_f32 : 0, in ? in->w : nullptr, in ? in->w_f32 : 0, in ? in->D : 0,
+        in ? in->logits_out : nullptr, M, E, top, expert_of, gate, counters);
     moe_offsets_kernel<<<1, 32, 0, stream>>>(counters, group_off, E);
     const int n = M * top;
     moe_scatter_kernel<<<(n + 255) / 256, 256, 0, stream>>>(expert_of, n, top, E, group_off, counters, sorted_tok, slot_of);

@@ -511,6 +511,19 @@ class MezilixEngine(_BatchOps):
     def set_option(self, name: str, value: int):
         check(lib().asd_mezilix_set_option(self.h, name.encode(), int(value)), "asd_mezilix_set_option")
 
+    PROFILE_CLASSES = ("dense", "head_products", "attention", "experts", "router", "glue", "lm_head")
+
+    def profile_read(self):
+        """(ms, launches) per kernel class since the last read; needs set_option('profile', 1)."""
+        n = len(self.PROFILE_CLASSES)
+        ms, cnt = (ctypes.c_float * n)(), (ctypes.c_int * n)()
+        check(lib().asd_mezilix_profile_read(self.h, ms, cnt, n), "asd_mezilix_profile_read")
+        return {c: (ms[i], cnt[i]) for i, c in enumerate(self.PROFILE_CLASSES)}
+
+    def check_device(self) -> None:
+        """raises if a kernel of this engine gave up a bounded wait (synchronises)"""
+        check(lib().asd_mezilix_device_error(self.h), "asd_mezilix_device_error")
+
     # ------------------------------------------------------------------ sequences
     def open_sequence(self) -> int:
         """a free slot (dynamic page table); its first forward starts at position 0, which resets the carried state"""

@@ -670,6 +670,140 @@ def run_ours(args):
         sys.exit(3)
 
 
+def family_sizes():
+    """(label, Mezilix config, Qwen2 config of the same width, depth, head count and active weights per layer)"""
+    from asd_b200.models.mezilix import sized_config
+    from asd_b200.models.qwen2 import Qwen2Config
+    out = []
+    for label, width, heads, layers in (("w2048", 2048, 16, 4), ("w4096", 4096, 32, 4)):
+        mz = sized_config(width, layers, heads, vocab=32768, dim=128, rot_dim=64, kv_rank=512, window=4096, experts=8,
+                          top=2, ff=width, name=f"mezilix-{label}")
+        l = mz.layers[0]
+        active = (l.q_rows + l.cache_row) * width + l.heads * (l.dim + l.vdim) * l.kv_rank + width * l.heads * l.vdim \
+            + l.top * 2 * l.ff * width
+        kv = max(1, heads // 8)
+        attn = (heads + 2 * kv) * 128 * width + heads * 128 * width
+        inter = max(256, int(round((active - attn) / (3 * width) / 256)) * 256)
+        qw = Qwen2Config(width, layers, heads, kv, inter, 32768, name=f"qwen2-{label}")
+        out.append((label, mz, qw))
+    return out
+
+
+def family_model(cfg, M, kv_len, nseq, peaks):
+    """algorithmic FLOPs and bytes of one forward of M tokens (nseq sequences, kv_len keys each) per kernel class"""
+    import math
+    L = cfg.num_hidden_layers
+    if getattr(cfg, "architecture", None) == "Mezilix":
+        l, D = cfg.layers[0], cfg.width
+        nqd, rw = l.q_rows + l.cache_row, l.cache_row
+        keys = min(l.window, kv_len)
+        w_dense = nqd * D + D * l.heads * l.vdim
+        w_heads = l.heads * (l.dim + l.vdim) * l.kv_rank
+        hit = l.experts * (1.0 - (1.0 - l.top / l.experts) ** M)
+        cls = {"dense": (2.0 * M * w_dense, 2.0 * w_dense + M * (2 * D + 4 * nqd + 2 * l.heads * l.vdim + 4 * D)),
+               "head_products": (2.0 * M * w_heads, 2.0 * w_heads + 4.0 * M * l.heads * (l.dim + rw + l.kv_rank) + 2.0 * M * l.heads * l.vdim),
+               "attention": (2.0 * M * l.heads * keys * (rw + l.kv_rank) * (0.5 if M > nseq else 1.0),
+                             2.0 * nseq * keys * rw + 4.0 * M * l.heads * (rw + l.kv_rank)),
+               "experts": (2.0 * M * l.top * 2 * l.ff * D, 2.0 * hit * 2 * l.ff * D + 2.0 * M * l.top * (D + 2 * l.ff) + 4.0 * M * l.top * D)}
+        head = (2.0 * nseq * cfg.vocab_size * D, 2.0 * cfg.vocab_size * D)
+    else:
+        D, H, KV, hd, I = cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
+        w = (H + 2 * KV) * hd * D + H * hd * D + 3 * D * I
+        cls = {"gemm": (2.0 * M * w, 2.0 * w + 2.0 * M * (4 * D + (H + 2 * KV) * hd + 3 * I)),
+               "attention": (4.0 * M * H * hd * kv_len * (0.5 if M > nseq else 1.0), 2.0 * nseq * kv_len * 2 * KV * hd + 4.0 * M * H * hd)}
+        head = (2.0 * nseq * cfg.vocab_size * D, 2.0 * cfg.vocab_size * D)
+    out = {}
+    for k, (fl, by) in cls.items():
+        out[k] = {"flops": fl * L, "bytes": by * L,
+                  "floor_ms": max(fl * L / (peaks["bf16_tflops"] * 1e12), by * L / (peaks["hbm_gbs"] * 1e9)) * 1e3}
+    out["lm_head"] = {"flops": head[0], "bytes": head[1],
+                      "floor_ms": max(head[0] / (peaks["bf16_tflops"] * 1e12), head[1] / (peaks["hbm_gbs"] * 1e9)) * 1e3}
+    return out
+
+
+def run_family(args):
+    """--family mezilix: prefill and decode throughput of the Mezilix engine at layer sizes of real models, beside the
+    Qwen2 engine at the same width, depth, head count and active weights per layer (random weights, synthetic tokens).
+    Per kernel class: device time (CUDA events around every launch) against its floor = max(FLOPs / measured cuBLAS bf16
+    rate, bytes / measured copy bandwidth).  Prints one JSON object; the default workload of this file is untouched."""
+    import torch
+    import asd_b200  # noqa: F401
+    from asd_b200.engine import MezilixEngine, QwenEngine
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks = json.load(open(path)) if os.path.exists(path) else {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)          # larger than the 126 MB L2
+    clocks = ClockSampler(0)
+    clocks.start()
+    records = []
+    ctx, pre_len = args.prefix if args.prefix != 512 else 2048, 1024
+    for label, mz_cfg, qw_cfg in family_sizes():
+        for fam, cfg in (("mezilix", mz_cfg), ("qwen2", qw_cfg)):
+            B = max(args.batch, 64)
+            kw = dict(max_seqs=B, max_seq_len=ctx + 64, max_tokens=4096, device=dev)
+            eng = (MezilixEngine(cfg, **kw) if fam == "mezilix" else QwenEngine(cfg, **kw)).load_random(seed=3)
+            g = torch.Generator().manual_seed(5)
+            rec = {"size": label, "family": fam, "model": cfg.name, "params_per_layer_active_M": None, "runs": []}
+
+            def timed(fn, n):
+                for _ in range(max(3, args.warmup)):
+                    fn()
+                torch.cuda.synchronize()
+                tot = 0.0
+                for _ in range(n):
+                    flush.zero_()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    fn()
+                    b.record()
+                    torch.cuda.synchronize()
+                    tot += a.elapsed_time(b)
+                eng.set_option("profile", 1)
+                fn()
+                prof = eng.profile_read()
+                eng.set_option("profile", 0)
+                return tot / n, prof
+
+            # prefill: 4 prompts of pre_len tokens from an empty cache, whole prompts in as few forwards as the engine takes
+            nseq = 4
+            prompts = torch.randint(0, cfg.vocab_size, (nseq, pre_len), generator=g).to(dev)
+            slots = torch.arange(nseq, dtype=torch.int32, device=dev)
+            ms, prof = timed(lambda: eng.prefill(prompts, slots), max(2, args.steps // 6))
+            model = family_model(cfg, nseq * pre_len, pre_len, nseq, peaks)
+            rec["runs"].append(_family_run("prefill", nseq, pre_len, nseq * pre_len, ms, prof, model))
+            # decode: one new token per sequence at a context of ctx tokens (the cache holds what the prefill and zeros left)
+            for nb in sorted({16, B}):
+                sl = torch.arange(nb, dtype=torch.int32, device=dev)
+                toks = torch.randint(0, cfg.vocab_size, (nb, 1), generator=g).to(torch.int32).to(dev)
+                start = torch.full((nb,), ctx - 1, dtype=torch.int32, device=dev)
+                ms, prof = timed(lambda: eng.forward_uniform(toks, start, sl, ctx), args.steps)
+                model = family_model(cfg, nb, ctx, nb, peaks)
+                rec["runs"].append(_family_run("decode", nb, ctx, nb, ms, prof, model))
+            records.append(rec)
+            eng.close()
+            del eng
+            torch.cuda.empty_cache()
+    clocks.stop_flag.set()
+    clocks.join()
+    print(json.dumps({"family_compare": records, "peaks": {k: peaks[k] for k in ("hbm_gbs", "bf16_tflops")},
+                      "timing": "CUDA events per forward, 256 MB L2 flush between timed forwards, warm-up >= 3",
+                      "clocks": clocks.summary(), "dtype": "bf16", "data": "synthetic tokens, random weights"}), flush=True)
+
+
+def _family_run(kind, nseq, length, tokens, ms, prof, model):
+    classes = {}
+    for c, (t, n) in prof.items():
+        if n == 0:
+            continue
+        m = model.get("gemm" if c in ("gemm",) else c)
+        classes[c] = {"ms": round(t, 4), "launches": n}
+        if m:
+            classes[c].update(floor_ms=round(m["floor_ms"], 4), of_floor=round(m["floor_ms"] / t, 3) if t > 0 else None)
+    return {"kind": kind, "sequences": nseq, "length": length, "tokens_per_forward": tokens, "ms": round(ms, 4),
+            "tokens_per_second": round(tokens / (ms * 1e-3), 1), "classes": classes}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -689,10 +823,14 @@ def main():
     ap.add_argument("--no-fuse-norm", action="store_true", help="separate add+RMSNorm kernels instead of the fused epilogues")
     ap.add_argument("--nccl-only", action="store_true", help="TP boundaries through ncclAllReduce instead of the fused kernel")
     ap.add_argument("--opt", action="append", help="engine option name=value (e.g. pdl=0, attn_impl=0)")
+    ap.add_argument("--family", default=None, choices=["mezilix"],
+                    help="instead of the default workload: prefill / decode throughput of this model family beside Qwen2 at equal size")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.family:
+        run_family(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -289,8 +289,10 @@ ASD_API int asd_mezilix_set_layer(asd_mezilix_engine_t* e, int layer, const void
 ASD_API size_t asd_mezilix_cache_bytes(const asd_mezilix_engine_t* e, int num_pages);
 ASD_API int asd_mezilix_set_cache(asd_mezilix_engine_t* e, void* pool, int num_pages, const int32_t* page_table,
                                   int max_seqs, int max_pages_per_seq, int32_t* token_ring, float* shift_ring);
-/* options: "tc_linear" (1, default: bf16 projections whose shape the tcgen05 weight-streaming GEMM accepts run on it;
- * 0: CUDA-core kernel everywhere), "tc_min_rows" (token count from which the tensor-bound CTA-pair GEMM is used) */
+/* options: "tc_linear" (1, default: bf16 projections whose shape the tcgen05 kernels accept run on them; 0: CUDA-core
+ * kernel everywhere), "tc_min_rows" (token count from which dense projections use the tensor-bound CTA-pair GEMM, default
+ * 257; 0 = never), "attn_tiled" (1, default: register-tiled attention kernel with key-range shares where the latent
+ * size allows; 0: one warp per (token, head)), "profile" (1: CUDA events around every launch, read with asd_mezilix_profile_read) */
 ASD_API int asd_mezilix_set_option(asd_mezilix_engine_t* e, const char* name, int value);
 /* Same contract as asd_engine_forward (M <= max_tokens).  layer_out (optional, fp32 [n_layers][M][width]) receives
  * the stream that leaves every layer. */
@@ -298,6 +300,9 @@ ASD_API int asd_mezilix_forward(asd_mezilix_engine_t* e, const int32_t* tokens, 
                                 const int32_t* token_slot, int M, const int32_t* cu_q, const int32_t* seq_slot, int nseq,
                                 int max_qlen, int max_kv_len, const int32_t* logit_rows, int n_logit_rows,
                                 float* logits_out, long long logits_ld, float* layer_out, void* stream);
+/* ms and launches by kernel class since the last read (nclass >= 7): 0 dense projections, 1 per-head latent products,
+ * 2 attention, 3 expert layers, 4 router, 5 embedding / shift / cache append / layer close, 6 output head */
+ASD_API int asd_mezilix_profile_read(asd_mezilix_engine_t* e, float* ms_by_class, int* launches_by_class, int nclass);
 /* non-zero (and an error message) if a kernel of this engine gave up a bounded wait since creation; synchronises */
 ASD_API int asd_mezilix_device_error(asd_mezilix_engine_t* e);
 /* Building blocks on their own (tests).  asd_linear_tc: y[z] = x[z] w[z]^T on tcgen05 with bf16 weights [Z][N][K], x

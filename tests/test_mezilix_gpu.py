@@ -244,7 +244,7 @@ def plant_pair(cfg, w, key_tok, query_tok, boost=600.0):
     w["l0.mix.q"] = q.reshape(H * (dn + dr), -1).to(torch.bfloat16)
 
 
-@pytest.mark.parametrize("window,page_size", [(9, 16), (16, 16), (33, 4), (300, 16), (257, 8)])
+@pytest.mark.parametrize("window,page_size", [(9, 16), (16, 16), (33, 4), (300, 16), (257, 8), (1000, 16)])
 def test_window_edges_with_standout_keys(window, page_size):
     """a key that outweighs everything else sits exactly window - 1 positions back (the last one visible) for one
     query and exactly window positions back (the first one hidden) for another, in a prompt and while decoding, far
@@ -272,13 +272,30 @@ def test_window_edges_with_standout_keys(window, page_size):
             assert rel_err(other[p:p + 1].float(), ref[p:p + 1])[1] > 0.3
     first_q = min(at_in + at_out)
     for cuts in ([n], [first_q - 1, 2, 1, 1, 37, 2, 1, 1], [first_q - 3] + [1] * (n - first_q + 3), [2] * (n // 2)):
-        eng = make_engine(cfg, w, max_tokens=512, page_size=page_size)
+        eng = make_engine(cfg, w, max_tokens=512, page_size=page_size, max_seq_len=1280)
         slot = eng.open_sequence()
         got = feed(eng, slot, ids, cuts)
         assert rel_err(got, ref)[1] < 3e-4
         for p in at_in + at_out:
             assert rel_err(got[p:p + 1], ref[p:p + 1])[1] < 3e-4
         eng.close()
+
+
+def test_both_attention_kernels_agree_with_the_oracle():
+    """the register-tiled kernel (with and without shares of the key range) and the one-warp-per-pair kernel on the
+    same long sequence: many heads, few heads, a latent size that fills no tile"""
+    for heads, kv_rank, rot_dim in ((6, 72, 12), (1, 32, 8), (20, 264, 4)):
+        cfg = config([layer(heads=heads, dim=8, rot_dim=rot_dim, vdim=8, kv_rank=kv_rank, window=700, scale=0.7, experts=0)])
+        w = O.random_model(cfg, seed=43, scale=2.0)
+        ids = tokens(900, 96, 44)
+        ref, _ = O.forward(cfg, w, ids)
+        for tiled in (1, 0):
+            eng = make_engine(cfg, w, max_tokens=1024, max_seq_len=1024)
+            eng.set_option("attn_tiled", tiled)
+            slot = eng.open_sequence()
+            got = feed(eng, slot, ids, [3, 830, 1, 1, 1, 2, 40, 1, 1])
+            assert rel_err(got, ref)[1] < 3e-4, (heads, tiled)
+            close(eng)
 
 
 def test_long_decoding_past_window_ring_and_pages():
