@@ -152,26 +152,38 @@ __global__ void __launch_bounds__(512) latent_attn_kernel(SeqIndex ix, const int
 // Register-tiled form for latent sizes that are multiples of 4 and at most 512 (RC = ceil(R / 256) <= 2).
 // One CTA = QT = 4 * RPT query rows (TQ consecutive tokens x HG heads of one sequence) x one share of the key tiles.
 // Per tile of 32 keys (fp32 in shared memory, row stride rw + 4 so that float4 reads of 8 different keys hit 32 banks):
-//   scores   thread (qq, kq) = (t / 16, t % 16): rows {qq, qq + 16} x keys {kq, kq + 16}, float4 steps over R + dr;
-//   softmax  warp w owns rows w * QT / 8 ..: running maximum and sum in registers, weights transposed to [key][row];
+//   scores   warp w owns rows w * QT / 8 .., lane = key: float4 steps over R + dr, the query values one broadcast read;
+//   softmax  in the same registers: running maximum and sum per row, weights written transposed as [key][row];
 //   update   thread (qg, rg) = (warp / 2, (warp % 2) * 32 + lane): rows qg * RPT .. x latent columns {4 rg + 256 i}:
 //            RPT x 4 RC accumulators fed by one float4 of weights (broadcast) and RC float4 of the key row per key.
 // A long key range is cut into shares (blockIdx.y = sequence * nsplit + share) so that few query rows still fill the
 // GPU; every share writes its unnormalised sum, maximum and weight sum, and latent_combine_kernel merges them.
+// 8 consecutive cache elements as fp32 (16-byte load for bf16 rows)
+__device__ __forceinline__ void widen8(const uint4& v, float* dst) {
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        dst[2 * i] = __uint_as_float(u[i] << 16);
+        dst[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+}
+
+// vec = 1 (bf16 rows of a multiple of 8 elements, 16-byte aligned pool): the next tile's rows are fetched into registers
+// with 16-byte loads while the current tile is computed, and widened to fp32 on the way into shared memory.
 template <typename T, int RPT, int RC>
-__global__ void __launch_bounds__(256) latent_attn_tiled(SeqIndex ix, const int* cu_q, const int* seq_slot, int TQ, int HG,
-                                                         int nsplit, const float* q_lat, LatentDims d, PagedRows cache,
-                                                         float* out_lat, float* ws_o, float* ws_ml) {
-    constexpr int QT = 4 * RPT, KT = 32, NQ = QT / 16, RW = QT / 8;
+__global__ void __launch_bounds__(256, 1) latent_attn_tiled(SeqIndex ix, const int* cu_q, const int* seq_slot, int TQ,
+                                                            int HG, int nsplit, int vec, const float* q_lat, LatentDims d,
+                                                            PagedRows cache, float* out_lat, float* ws_o, float* ws_ml) {
+    constexpr int QT = 4 * RPT, KT = 32, RW = QT / 8;
     extern __shared__ float smem[];
     const int rw = d.R + d.dr, LD = rw + 4;
     float* Ks = smem;                        // [KT][LD]
     float* Qs = Ks + KT * LD;                // [QT][LD]
-    float* Ss = Qs + QT * LD;                // [QT][KT + 1]
-    float* Pt = Ss + QT * (KT + 1);          // [KT][QT]
+    float* Pt = Qs + QT * LD;                // [KT][QT] softmax weights of the tile, transposed
     float* Cs = Pt + KT * QT;                // [QT] rescale of this tile, then the final weight sums
     float* Ms = Cs + QT;                     // [QT] final maxima
     __shared__ int row_pos[32];
+    __shared__ long long key_row[2][32];     // pool rows of the keys of tile t in key_row[t & 1] (-1: past the last position)
     const int seq = blockIdx.y / nsplit, split = blockIdx.y % nsplit;
     const int t0 = cu_q[seq] + blockIdx.x * TQ, t_end = cu_q[seq + 1];
     if (t0 >= t_end) return;
@@ -204,65 +216,102 @@ __global__ void __launch_bounds__(256) latent_attn_tiled(SeqIndex ix, const int*
     float m_run[RW], l_run[RW];
 #pragma unroll
     for (int i = 0; i < RW; ++i) m_run[i] = -INFINITY, l_run[i] = 0.f;
-    const int kq = tid & 15, qq = tid >> 4;
     const int qg = warp >> 1, rg = (warp & 1) * 32 + lane;
     const T* pool = (const T*)cache.pool;
+    constexpr int MAXCH = 13;                // 32 rows x (rw / 8) chunks over 256 threads, rw <= 828
+    uint4 pre[MAXCH];
+    const int cpr = rw >> 3, nch = KT * cpr;
+    auto fetch = [&](int t) {
+#pragma unroll
+        for (int i = 0; i < MAXCH; ++i) {
+            const int idx = tid + 256 * i;
+            if (idx < nch) {
+                const int r = idx / cpr, c = idx - r * cpr;
+                const long long row = key_row[t & 1][r];
+                pre[i] = row >= 0 ? *reinterpret_cast<const uint4*>(pool + row * rw + 8 * c) : make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    // the page-table lookups run one tile ahead of the loads that need them
+    auto locate = [&](int t) {
+        if (tid < KT) {
+            const int kp = j_lo + t * KT + tid;
+            key_row[t & 1][tid] = (t < te && kp <= p_last) ? cache_row(cache, slot, kp) : -1;
+        }
+    };
+    if (vec && ts < te) {
+        locate(ts);
+        locate(ts + 1);
+        __syncthreads();
+        fetch(ts);
+    }
     for (int t = ts; t < te; ++t) {
         const int j0 = j_lo + t * KT;
         __syncthreads();                     // the previous tile is consumed; Qs and row_pos are written
-        for (int r = warp; r < KT; r += 8) {
-            const int kp = j0 + r;
-            if (kp <= p_last) {
-                const T* src = pool + cache_row(cache, slot, kp) * rw;
-                for (int i = lane; i < rw; i += 32) Ks[r * LD + i] = ldf(src + i);
-            } else {
-                for (int i = lane; i < rw; i += 32) Ks[r * LD + i] = 0.f;
+        if (vec) {
+#pragma unroll
+            for (int i = 0; i < MAXCH; ++i) {
+                const int idx = tid + 256 * i;
+                if (idx < nch) {
+                    const int r = idx / cpr, c = idx - r * cpr;
+                    float f[8];
+                    widen8(pre[i], f);
+                    *reinterpret_cast<float4*>(Ks + r * LD + 8 * c) = make_float4(f[0], f[1], f[2], f[3]);
+                    *reinterpret_cast<float4*>(Ks + r * LD + 8 * c + 4) = make_float4(f[4], f[5], f[6], f[7]);
+                }
+            }
+            if (t + 1 < te) fetch(t + 1);    // in flight while this tile is computed
+            locate(t + 2);                   // key_row[t & 1] was last read by fetch(t), before this tile's first barrier
+        } else {
+            for (int r = warp; r < KT; r += 8) {
+                const int kp = j0 + r;
+                const T* src = kp <= p_last ? pool + cache_row(cache, slot, kp) * rw : nullptr;
+                for (int i = lane; i < rw; i += 128) {      // four loads in flight per lane
+                    float v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) v[u] = (src && i + 32 * u < rw) ? ldf(src + i + 32 * u) : 0.f;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (i + 32 * u < rw) Ks[r * LD + i + 32 * u] = v[u];
+                }
             }
         }
         __syncthreads();
-        {   // scores
-            float s[NQ][2];
+        // scores and softmax bookkeeping: warp w owns rows w * RW .., lane = key of the tile.  The query values are the
+        // same address for the whole warp (one shared-memory wavefront); the 32 key rows are 32 different bank groups.
+        {
+            float s[RW][2];
 #pragma unroll
-            for (int a = 0; a < NQ; ++a) s[a][0] = s[a][1] = 0.f;
-            const float* k0 = Ks + kq * LD;
-            const float* k1 = Ks + (kq + 16) * LD;
+            for (int a = 0; a < RW; ++a) s[a][0] = s[a][1] = 0.f;
+            const float* kr = Ks + lane * LD;
+            const float* qr = Qs + warp * RW * LD;
+#pragma unroll 4
             for (int i = 0; i < rw; i += 4) {
-                const float4 ka = *reinterpret_cast<const float4*>(k0 + i), kb = *reinterpret_cast<const float4*>(k1 + i);
+                const float4 kv = *reinterpret_cast<const float4*>(kr + i);
 #pragma unroll
-                for (int a = 0; a < NQ; ++a) {
-                    const float4 q = *reinterpret_cast<const float4*>(Qs + (qq + 16 * a) * LD + i);
-                    s[a][0] = fmaf(q.x, ka.x, s[a][0]), s[a][0] = fmaf(q.y, ka.y, s[a][0]);
-                    s[a][0] = fmaf(q.z, ka.z, s[a][0]), s[a][0] = fmaf(q.w, ka.w, s[a][0]);
-                    s[a][1] = fmaf(q.x, kb.x, s[a][1]), s[a][1] = fmaf(q.y, kb.y, s[a][1]);
-                    s[a][1] = fmaf(q.z, kb.z, s[a][1]), s[a][1] = fmaf(q.w, kb.w, s[a][1]);
+                for (int a = 0; a < RW; ++a) {
+                    const float4 q = *reinterpret_cast<const float4*>(qr + a * LD + i);
+                    s[a][0] = fmaf(q.x, kv.x, s[a][0]), s[a][1] = fmaf(q.y, kv.y, s[a][1]);
+                    s[a][0] = fmaf(q.z, kv.z, s[a][0]), s[a][1] = fmaf(q.w, kv.w, s[a][1]);
                 }
             }
+            const int kp = j0 + lane;
 #pragma unroll
-            for (int a = 0; a < NQ; ++a) {
-                const int r = qq + 16 * a, p = row_pos[r];
-#pragma unroll
-                for (int b = 0; b < 2; ++b) {
-                    const int kp = j0 + kq + 16 * b;
-                    const bool seen = p >= 0 && kp <= p && p - kp < d.window;
-                    Ss[r * (KT + 1) + kq + 16 * b] = seen ? s[a][b] * d.scale : -INFINITY;
+            for (int a = 0; a < RW; ++a) {
+                const int r = warp * RW + a, p = row_pos[r];
+                const bool seen = p >= 0 && kp <= p && p - kp < d.window;
+                const float sv = seen ? (s[a][0] + s[a][1]) * d.scale : -INFINITY;
+                const float m_new = fmaxf(m_run[a], warp_max(sv));
+                float corr = 1.f, w = 0.f;
+                if (m_new != -INFINITY) {
+                    corr = expf(m_run[a] - m_new);      // exp(-inf) = 0 on the row's first visible tile
+                    w = seen ? expf(sv - m_new) : 0.f;
                 }
+                l_run[a] = l_run[a] * corr + warp_sum(w);
+                m_run[a] = m_new;
+                Pt[lane * QT + r] = w;
+                if (lane == 0) Cs[r] = corr;
             }
-        }
-        __syncthreads();
-#pragma unroll
-        for (int i = 0; i < RW; ++i) {       // softmax bookkeeping of this warp's rows
-            const int r = warp * RW + i;
-            const float sv = Ss[r * (KT + 1) + lane];
-            const float m_new = fmaxf(m_run[i], warp_max(sv));
-            float corr = 1.f, w = 0.f;
-            if (m_new != -INFINITY) {
-                corr = expf(m_run[i] - m_new);      // exp(-inf) = 0 on the row's first visible tile
-                w = sv == -INFINITY ? 0.f : expf(sv - m_new);
-            }
-            l_run[i] = l_run[i] * corr + warp_sum(w);
-            m_run[i] = m_new;
-            Pt[lane * QT + r] = w;
-            if (lane == 0) Cs[r] = corr;
         }
         __syncthreads();
         {   // update
@@ -274,6 +323,7 @@ __global__ void __launch_bounds__(256) latent_attn_tiled(SeqIndex ix, const int*
 #pragma unroll
                 for (int j = 0; j < RC; ++j)
                     acc[i][j].x *= cr[i], acc[i][j].y *= cr[i], acc[i][j].z *= cr[i], acc[i][j].w *= cr[i];
+#pragma unroll 2
             for (int k = 0; k < KT; ++k) {
                 float w[RPT];
 #pragma unroll
@@ -358,7 +408,7 @@ int launch_tiled_t(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int
     int TQ = QT / HG;
     if (TQ > max_qlen) TQ = max_qlen;
     const int rw = d.R + d.dr, LD = rw + 4;
-    const size_t smem = (size_t)(32 * LD + QT * LD + QT * 33 + 32 * QT + 2 * QT) * sizeof(float);
+    const size_t smem = (size_t)(32 * LD + QT * LD + 32 * QT + 2 * QT) * sizeof(float);
     const int q_tiles = (max_qlen + TQ - 1) / TQ, hgs = (d.heads + HG - 1) / HG;
     // shares of the key range: enough CTAs for two per SM, at least four key tiles each, within the workspace
     long long keys = (long long)(d.window < max_kv_len ? d.window : max_kv_len) + TQ;
@@ -376,7 +426,8 @@ int launch_tiled_t(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int
     auto fn = latent_attn_tiled<T, RPT, RC>;
     ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(q_tiles, nseq * nsplit, hgs);
-    fn<<<grid, 256, smem, stream>>>(ix, cu_q, seq_slot, TQ, HG, nsplit, q_lat, d, cache, out_lat, ws.o, ws.ml);
+    const int vec = sizeof(T) == 2 && (rw & 7) == 0 && (reinterpret_cast<uintptr_t>(cache.pool) & 15) == 0;
+    fn<<<grid, 256, smem, stream>>>(ix, cu_q, seq_slot, TQ, HG, nsplit, vec, q_lat, d, cache, out_lat, ws.o, ws.ml);
     count_launch(1);
     if (nsplit > 1) {
         latent_combine_kernel<<<(unsigned)rows, 128, 0, stream>>>(ws.o, ws.ml, nsplit, d.R, out_lat);

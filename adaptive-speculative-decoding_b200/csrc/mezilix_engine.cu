@@ -179,7 +179,7 @@ static int forward(MzEngine* e, const int* tokens, const int* positions, const i
         if (c.experts > 0) {
             {   // router logits in fp32 on the CUDA cores in both modes, fused with the softmax and the choice
                 MZ_PROF(MZ_ROUTER);
-                const MoeRouterInput in{e->h, f32, ly.router, f32, D, nullptr};
+                const MoeRouterInput in{e->h, f32, ly.router, f32, D, e->rlog};
                 if (launch_moe_route(nullptr, &in, M, c.experts, c.top, e->expert_of, e->gate, e->counters, e->group_off,
                                      e->sorted_tok, e->slot_of, s))
                     return -1;

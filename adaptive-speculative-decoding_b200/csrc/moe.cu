@@ -89,6 +89,35 @@ __global__ void moe_route_kernel(const float* logits, const void* x, int xf32, c
     }
 }
 
+// router logits, one CTA per token: z[m][e] = sum_d x[m][d] * wr[e][d] in fp32.  Thread t sums d = t, t + 128, ... in
+// increasing order, then the fixed warp tree and the warps in index order: a token's logits do not depend on the batch.
+__global__ void __launch_bounds__(128) moe_logits_kernel(const void* x, int xf32, const void* wr, int wf32, int D, int E,
+                                                         float* z_out) {
+    __shared__ float red[4][8];
+    const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int e0 = 0; e0 < E; e0 += 8) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int d = threadIdx.x; d < D; d += 128) {
+            const float xv = ldx(x, (long long)m * D + d, xf32);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (e0 + j < E) acc[j] = fmaf(xv, ldx(wr, (long long)(e0 + j) * D + d, wf32), acc[j]);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float v = warp_sum(acc[j]);
+            if (lane == 0) red[warp][j] = v;
+        }
+        __syncthreads();
+        if (threadIdx.x < 8 && e0 + threadIdx.x < E)
+            z_out[(long long)m * E + e0 + threadIdx.x] =
+                ((red[0][threadIdx.x] + red[1][threadIdx.x]) + red[2][threadIdx.x]) + red[3][threadIdx.x];
+    }
+}
+
 __global__ void moe_offsets_kernel(int* counters, int* group_off, int E) {
     if (threadIdx.x == 0) {
         int o = 0;
@@ -120,9 +149,15 @@ int launch_moe_route(const float* logits, const MoeRouterInput* in, int M, int E
     if ((size_t)E * 8 * sizeof(float) > 48 * 1024) return set_error("moe: more than 1536 experts");
     if (!logits && !in) return set_error("moe: neither logits nor router inputs");
     ASD_CUDA(cudaMemsetAsync(counters, 0, sizeof(int) * E, stream));
+    if (in && in->logits_out) {          // a CTA per token for the logits: few tokens still spread over the GPU
+        moe_logits_kernel<<<M, 128, 0, stream>>>(in->x, in->x_f32, in->w, in->w_f32, in->D, E, in->logits_out);
+        count_launch(1);
+        logits = in->logits_out;
+        in = nullptr;
+    }
     moe_route_kernel<<<(M + 3) / 4, 128, (size_t)E * 8 * sizeof(float), stream>>>(
         logits, in ? in->x : nullptr, in ? in->x_f32 : 0, in ? in->w : nullptr, in ? in->w_f32 : 0, in ? in->D : 0,
-        in ? in->logits_out : nullptr, M, E, top, expert_of, gate, counters);
+        nullptr, M, E, top, expert_of, gate, counters);
     moe_offsets_kernel<<<1, 32, 0, stream>>>(counters, group_off, E);
     const int n = M * top;
     moe_scatter_kernel<<<(n + 255) / 256, 256, 0, stream>>>(expert_of, n, top, E, group_off, counters, sorted_tok, slot_of);

@@ -275,9 +275,10 @@ def test_window_edges_with_standout_keys(window, page_size):
         eng = make_engine(cfg, w, max_tokens=512, page_size=page_size, max_seq_len=1280)
         slot = eng.open_sequence()
         got = feed(eng, slot, ids, cuts)
-        assert rel_err(got, ref)[1] < 3e-4
+        # planted scores are about 600, where one fp32 ulp is 6e-5: the weights carry that rounding, an off-by-one 0.3
+        assert rel_err(got, ref)[1] < 1e-3
         for p in at_in + at_out:
-            assert rel_err(got[p:p + 1], ref[p:p + 1])[1] < 3e-4
+            assert rel_err(got[p:p + 1], ref[p:p + 1])[1] < 1e-3
         eng.close()
 
 
