@@ -447,3 +447,53 @@ def test_speculative_decoding_with_a_mezilix_draft_equals_plain_greedy():
         return toks.tolist()
 
     assert run(True) == run(False)
+
+
+def write_checkpoint(path, cfg_dict, w):
+    """config.json + model.safetensors (8-byte little-endian header length, JSON header, raw data)"""
+    import json
+    import struct
+    path.mkdir()
+    (path / "config.json").write_text(json.dumps(cfg_dict))
+    header, blobs, off = {}, [], 0
+    for name, t in w.items():
+        raw = t.contiguous().view(torch.uint8).numpy().tobytes() if t.dim() else t.reshape(1).view(torch.uint8).numpy().tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    hj = json.dumps(header).encode()
+    with open(path / "model.safetensors", "wb") as f:
+        f.write(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_command_on_a_checkpoint_directory(tmp_path, dtype):
+    """the command-line runner end to end: registry by config.json, safetensors loader, page table with two requests one
+    after the other (the second reuses the first one's slot and pages), portions down to one token, wanted rows only"""
+    import json
+    import os
+    import subprocess
+    import sys
+    import numpy as np
+    w = O.random_model(ODD, seed=51)
+    write_checkpoint(tmp_path / "model", ODD, w)
+    a, b = tokens(41, ODD["vocab"], 52), tokens(23, ODD["vocab"], 53)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[30:32], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[32:33], "want": [0]}], "end": []},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[33:], "want": [7, 3]}], "end": ["a"]},
+             {"step": 4, "entries": [{"id": "b", "tokens": b, "want": [22]}], "end": ["b"]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path / "model"), "--dtype",
+                        dtype, "--out", str(out), "--max-tokens", "48"], input="\n".join(json.dumps(x) for x in steps) + "\n",
+                       capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.split("\n") if l.startswith("done")] == [f"done {i}" for i in range(5)]
+    ra, rb = O.forward(ODD, w, a)[0], O.forward(ODD, w, b)[0]
+    want = {0: ra[[0, 29]], 2: ra[[32]], 3: ra[[40, 36]], 4: rb[[22]]}
+    assert not (out / "1.f32").exists()
+    tol = 2e-4 if dtype == "float32" else 5e-2
+    for step, ref in want.items():
+        got = torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(ref.shape[0], -1).copy())
+        assert rel_err(got, ref)[1] < tol, step
