@@ -441,8 +441,10 @@ class MezilixEngine(_BatchOps):
         self.tp_rank, self.tp_size = 0, 1
         self.max_seqs, self.max_seq_len, self.max_tokens, self.page_size = max_seqs, max_seq_len, max_tokens, page_size
         self.ring = int(ring)
-        self.c = MezilixConfigC(cfg.width, cfg.vocab_size, cfg.num_hidden_layers, cfg.eps, cfg.buckets, cfg.mul_prev,
-                                cfg.mul_cur, max_tokens, page_size, self.ring, 1 if dtype == torch.float32 else 0)
+        # the multipliers enter modulo the table size: the same rows, and 32-bit fields hold any configured value
+        self.c = MezilixConfigC(cfg.width, cfg.vocab_size, cfg.num_hidden_layers, cfg.eps, cfg.buckets,
+                                cfg.mul_prev % cfg.buckets, cfg.mul_cur % cfg.buckets, max_tokens, page_size, self.ring,
+                                1 if dtype == torch.float32 else 0)
         arr = (MezilixLayerC * max(1, cfg.num_hidden_layers))()
         for i, l in enumerate(cfg.layers):
             arr[i] = MezilixLayerC(l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.window, l.rot_base,

@@ -346,6 +346,29 @@ def test_bf16_engine_both_linear_paths(tc):
     close(eng)
 
 
+# multiples of 8 that fill no tile of 64 (tensor-core paths with ragged edges); a latent row of 44 elements (multiple of
+# 4, not of 8: register-tiled attention without 16-byte cache loads); multipliers beyond 32 bits
+EIGHTS = config([layer(heads=3, dim=24, rot_dim=8, vdim=40, kv_rank=88, window=21, experts=3, top=2, ff=56),
+                 layer(heads=2, dim=16, rot_dim=8, vdim=8, kv_rank=36, window=400, experts=0)],
+                width=72, vocab=104, buckets=31, mul_prev=(1 << 40) + 7, mul_cur=(1 << 33) + 5)
+
+
+@pytest.mark.parametrize("cfg_dict", [ODD, EIGHTS], ids=["odd", "eights"])
+def test_bf16_engine_on_sizes_that_fill_no_tile(cfg_dict):
+    w = O.random_model(cfg_dict, seed=37)
+    ids = tokens(120, cfg_dict["vocab"], 38)
+    ref, _ = O.forward(cfg_dict, w, ids)
+    eng32 = make_engine(cfg_dict, w, max_tokens=128)
+    exact = feed(eng32, eng32.open_sequence(), ids, [])
+    assert rel_err(exact, ref)[1] < 2e-4
+    close(eng32)
+    for cuts in ([], [70, 2, 9] + [1] * 39):
+        eng = make_engine(cfg_dict, w, dtype=torch.bfloat16, max_tokens=128)
+        got = feed(eng, eng.open_sequence(), ids, cuts)
+        assert rel_err(got, ref)[0] < 4e-2, cuts[:3]
+        close(eng)
+
+
 def test_linear_on_cuda_cores_matches_fp32_matmul():
     from asd_b200._lib import check, lib
     g = torch.Generator().manual_seed(29)
