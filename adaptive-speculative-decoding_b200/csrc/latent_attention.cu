@@ -280,9 +280,9 @@ __global__ void __launch_bounds__(256, 1) latent_attn_tiled(SeqIndex ix, const i
         // scores and softmax bookkeeping: warp w owns rows w * RW .., lane = key of the tile.  The query values are the
         // same address for the whole warp (one shared-memory wavefront); the 32 key rows are 32 different bank groups.
         {
-            float s[RW][2];
+            float s[RW][4];                  // four partial sums per row: independent FMA chains
 #pragma unroll
-            for (int a = 0; a < RW; ++a) s[a][0] = s[a][1] = 0.f;
+            for (int a = 0; a < RW; ++a) s[a][0] = s[a][1] = s[a][2] = s[a][3] = 0.f;
             const float* kr = Ks + lane * LD;
             const float* qr = Qs + warp * RW * LD;
 #pragma unroll 4
@@ -292,7 +292,7 @@ __global__ void __launch_bounds__(256, 1) latent_attn_tiled(SeqIndex ix, const i
                 for (int a = 0; a < RW; ++a) {
                     const float4 q = *reinterpret_cast<const float4*>(qr + a * LD + i);
                     s[a][0] = fmaf(q.x, kv.x, s[a][0]), s[a][1] = fmaf(q.y, kv.y, s[a][1]);
-                    s[a][0] = fmaf(q.z, kv.z, s[a][0]), s[a][1] = fmaf(q.w, kv.w, s[a][1]);
+                    s[a][2] = fmaf(q.z, kv.z, s[a][2]), s[a][3] = fmaf(q.w, kv.w, s[a][3]);
                 }
             }
             const int kp = j0 + lane;
@@ -300,7 +300,7 @@ __global__ void __launch_bounds__(256, 1) latent_attn_tiled(SeqIndex ix, const i
             for (int a = 0; a < RW; ++a) {
                 const int r = warp * RW + a, p = row_pos[r];
                 const bool seen = p >= 0 && kp <= p && p - kp < d.window;
-                const float sv = seen ? (s[a][0] + s[a][1]) * d.scale : -INFINITY;
+                const float sv = seen ? ((s[a][0] + s[a][1]) + (s[a][2] + s[a][3])) * d.scale : -INFINITY;
                 const float m_new = fmaxf(m_run[a], warp_max(sv));
                 float corr = 1.f, w = 0.f;
                 if (m_new != -INFINITY) {
@@ -410,13 +410,19 @@ int launch_tiled_t(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int
     const int rw = d.R + d.dr, LD = rw + 4;
     const size_t smem = (size_t)(32 * LD + QT * LD + 32 * QT + 2 * QT) * sizeof(float);
     const int q_tiles = (max_qlen + TQ - 1) / TQ, hgs = (d.heads + HG - 1) / HG;
-    // shares of the key range: enough CTAs for two per SM, at least four key tiles each, within the workspace
+    // shares of the key range: at most two full waves of one CTA per SM (a third, mostly empty wave costs more than the
+    // longer key loop of fewer shares), at least four key tiles each, within the workspace
     long long keys = (long long)(d.window < max_kv_len ? d.window : max_kv_len) + TQ;
     const int kv_tiles = (int)((keys + 31) / 32);
     int nsplit = 1;
     const long long ctas = (long long)q_tiles * nseq * hgs, rows = (long long)ix.M * d.heads;
-    if (ws.o && ws.ml && ctas < 296) {
-        nsplit = (int)((296 + ctas - 1) / ctas);
+    static const int two_waves = []() {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        return 2 * sms;
+    }();
+    if (ws.o && ws.ml && ctas < two_waves) {
+        nsplit = (int)(two_waves / ctas);
         if (nsplit > kv_tiles / 4) nsplit = kv_tiles / 4;
         if ((long long)nsplit * rows > ws.rows) nsplit = (int)(ws.rows / rows);
         if ((long long)nsplit * rows * d.R > ws.o_elems) nsplit = (int)(ws.o_elems / (rows * d.R));
