@@ -106,12 +106,13 @@ int launch_latent_post(const SeqIndex& ix, const float* qd, const LatentDims& d,
                        const float* inv_freq, const PagedRows& cache, float* q_lat, cudaStream_t stream);
 // Workspace of the register-tiled kernel when it cuts a long key range into shares (few query rows, long context):
 // o [o_elems] floats, ml [2 * rows] floats; (token, head) pairs x shares must fit `rows`.  tiled = 0 forces the
-// one-warp-per-pair kernel, which takes any latent size.
+// one-warp-per-pair kernel, which takes any latent size; 1 the register-tiled fp32 kernel where the sizes allow; 2 (default)
+// lets bf16 cache rows run on the tensor cores with the fp32 operands split into two bf16 terms.
 struct AttnSplit {
     float* o = nullptr;
     float* ml = nullptr;
     long long rows = 0, o_elems = 0;
-    int tiled = 1;
+    int tiled = 2;
 };
 // out_lat fp32 [M][heads][R].  cu_q / seq_slot as in asd_engine_forward; a sequence's tokens are consecutive positions;
 // max_kv_len bounds position + 1 over the batch.

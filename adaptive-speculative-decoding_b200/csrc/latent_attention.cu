@@ -379,6 +379,244 @@ __global__ void __launch_bounds__(256, 1) latent_attn_tiled(SeqIndex ix, const i
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-core form for bf16 cache rows (latent size a multiple of 8 and at most 512, row length a multiple of 16):
+// the two products of a tile run as mma.sync m16n8k16 with fp32 accumulation, and the fp32 operand of each (the query
+// in latent space, the softmax weights) enters as a sum of bf16 terms, x = hi + mid + lo with hi = bf16(x), mid =
+// bf16(x - hi), lo = bf16(x - hi - mid): three terms carry all 24 bits of the query, so a score is the same fp32 sum of
+// exact products the CUDA-core kernel forms; the weights take two terms (16 bits) into the product with the bf16 values.  One CTA = 16 query rows (tokens x heads of one sequence) x one share of the keys,
+// 64 keys per tile: warp w scores keys 8 w .. 8 w + 7 over the whole row length, the scores meet in shared memory for
+// the running softmax (warp w owns rows 2 w, 2 w + 1), and warp w then updates the latent columns of the 8-wide tiles
+// w, w + 8, ... with the key rows read through ldmatrix.trans.
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& b0, uint32_t& b1, const void* smem_row) {
+    const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+}
+__device__ __forceinline__ void split_bf16(float x, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+    hi = __float2bfloat16(x);
+    lo = __float2bfloat16(x - __bfloat162float(hi));
+}
+
+__global__ void __launch_bounds__(256, 1) latent_attn_mma(SeqIndex ix, const int* cu_q, const int* seq_slot, int TQ, int HG,
+                                                          int nsplit, const float* q_lat, LatentDims d, PagedRows cache,
+                                                          float* out_lat, float* ws_o, float* ws_ml) {
+    constexpr int QT = 16, KT = 64, NTW = 8;                  // NTW: 8-wide latent tiles per warp (R <= 512)
+    extern __shared__ __align__(16) uint8_t smem_b[];
+    const int rw = d.R + d.dr, LDK = rw + 8;                  // bf16 elements per staged row (16-byte multiple)
+    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_b);          // [KT][LDK]
+    __nv_bfloat16* Qh = Ks + KT * LDK;                                     // [QT][LDK]
+    __nv_bfloat16* Qm = Qh + QT * LDK;                                     // [QT][LDK]
+    __nv_bfloat16* Ql = Qm + QT * LDK;                                     // [QT][LDK]
+    __nv_bfloat16* Ph = Ql + QT * LDK;                                     // [QT][KT + 8]
+    __nv_bfloat16* Pl = Ph + QT * (KT + 8);                                // [QT][KT + 8]
+    float* Ss = reinterpret_cast<float*>(Pl + QT * (KT + 8));              // [QT][KT + 1]
+    float* Cs = Ss + QT * (KT + 1);                                        // [QT]
+    float* Ms = Cs + QT;                                                   // [QT]
+    __shared__ int row_pos[QT];
+    __shared__ long long key_row[2][KT];
+    const int seq = blockIdx.y / nsplit, split = blockIdx.y % nsplit;
+    const int t0 = cu_q[seq] + blockIdx.x * TQ, t_end = cu_q[seq + 1];
+    if (t0 >= t_end) return;
+    const int slot = seq_slot[seq];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq4 = lane & 3;
+    const int n_tok = min(TQ, t_end - t0), h0 = blockIdx.z * HG;
+    const int p_first = ix.positions[t0], p_last = ix.positions[t0 + n_tok - 1];
+    int j_lo = p_first - d.window + 1;
+    if (j_lo < 0) j_lo = 0;
+    const int nt = (p_last - j_lo) / KT + 1, per = (nt + nsplit - 1) / nsplit;
+    const int ts = split * per, te = min(nt, ts + per);
+    if (tid < QT) {
+        const int tq = tid / HG, h = h0 + tid % HG;
+        row_pos[tid] = (tq < n_tok && h < d.heads && tid < TQ * HG) ? ix.positions[t0 + tq] : -1;
+    }
+    {   // the query rows as three bf16 terms (24 bits); four 16-byte loads in flight per thread
+        const int cpq = rw >> 2, total = QT * cpq;
+        for (int base = 0; base < total; base += 1024) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = base + tid + 256 * u;
+                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i < total) {
+                    const int r = i / cpq, c = i - r * cpq;
+                    const int tq = r / HG, h = h0 + r % HG;
+                    if (tq < n_tok && h < d.heads && r < TQ * HG)
+                        v[u] = *reinterpret_cast<const float4*>(q_lat + ((long long)(t0 + tq) * d.heads + h) * rw + 4 * c);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = base + tid + 256 * u;
+                if (i < total) {
+                    const int r = i / cpq, c = i - r * cpq;
+                    const float x[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int o = r * LDK + 4 * c + e;
+                        split_bf16(x[e], Qh[o], Qm[o]);
+                        const float rest = (x[e] - __bfloat162float(Qh[o])) - __bfloat162float(Qm[o]);
+                        Ql[o] = __float2bfloat16(rest);
+                    }
+                }
+            }
+        }
+    }
+    float acc[NTW][4];
+#pragma unroll
+    for (int i = 0; i < NTW; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const __nv_bfloat16* pool = (const __nv_bfloat16*)cache.pool;
+    constexpr int MAXCH = 26;                                 // 64 rows x (rw / 8) chunks over 256 threads, rw <= 832
+    uint4 pre[MAXCH];
+    const int cpr = rw >> 3, nch = KT * cpr;
+    auto fetch = [&](int t) {
+#pragma unroll
+        for (int i = 0; i < MAXCH; ++i) {
+            const int idx = tid + 256 * i;
+            if (idx < nch) {
+                const int r = idx / cpr, c = idx - r * cpr;
+                const long long row = key_row[t & 1][r];
+                pre[i] = row >= 0 ? *reinterpret_cast<const uint4*>(pool + row * rw + 8 * c) : make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    auto locate = [&](int t) {
+        if (tid < KT) {
+            const int kp = j_lo + t * KT + tid;
+            key_row[t & 1][tid] = (t < te && kp <= p_last) ? cache_row(cache, slot, kp) : -1;
+        }
+    };
+    if (ts < te) {
+        locate(ts);
+        locate(ts + 1);
+        __syncthreads();
+        fetch(ts);
+    }
+    const int n_tiles_r = d.R >> 3;
+    for (int t = ts; t < te; ++t) {
+        const int j0 = j_lo + t * KT;
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < MAXCH; ++i) {
+            const int idx = tid + 256 * i;
+            if (idx < nch) {
+                const int r = idx / cpr, c = idx - r * cpr;
+                *reinterpret_cast<uint4*>(Ks + r * LDK + 8 * c) = pre[i];
+            }
+        }
+        if (t + 1 < te) fetch(t + 1);
+        locate(t + 2);
+        __syncthreads();
+        {   // scores of keys 8 warp .. 8 warp + 7 for all 16 rows
+            float st[3][4];                  // one accumulator per term: three independent MMA chains
+#pragma unroll
+            for (int u = 0; u < 3; ++u) st[u][0] = st[u][1] = st[u][2] = st[u][3] = 0.f;
+            const __nv_bfloat16* kb = Ks + (warp * 8 + g) * LDK + 2 * tq4;
+            const __nv_bfloat16* qt[3] = {Qh + g * LDK + 2 * tq4, Qm + g * LDK + 2 * tq4, Ql + g * LDK + 2 * tq4};
+#pragma unroll 2
+            for (int k0 = 0; k0 < rw; k0 += 16) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + k0), b1 = *reinterpret_cast<const uint32_t*>(kb + k0 + 8);
+#pragma unroll
+                for (int u = 0; u < 3; ++u) {
+                    uint32_t a[4];
+                    a[0] = *reinterpret_cast<const uint32_t*>(qt[u] + k0);
+                    a[1] = *reinterpret_cast<const uint32_t*>(qt[u] + 8 * LDK + k0);
+                    a[2] = *reinterpret_cast<const uint32_t*>(qt[u] + k0 + 8);
+                    a[3] = *reinterpret_cast<const uint32_t*>(qt[u] + 8 * LDK + k0 + 8);
+                    mma_bf16(st[u], a, b0, b1);
+                }
+            }
+            float sc[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sc[e] = st[0][e] + (st[1][e] + st[2][e]);
+            const int col = warp * 8 + 2 * tq4;
+            Ss[g * (KT + 1) + col] = sc[0], Ss[g * (KT + 1) + col + 1] = sc[1];
+            Ss[(g + 8) * (KT + 1) + col] = sc[2], Ss[(g + 8) * (KT + 1) + col + 1] = sc[3];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int a = 0; a < 2; ++a) {        // running softmax of rows 2 warp, 2 warp + 1; lane = keys lane, lane + 32
+            const int r = warp * 2 + a, p = row_pos[r];
+            float sv[2], w[2];
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                const int kp = j0 + lane + 32 * b;
+                const bool seen = p >= 0 && kp <= p && p - kp < d.window;
+                sv[b] = seen ? Ss[r * (KT + 1) + lane + 32 * b] * d.scale : -INFINITY;
+            }
+            const float m_new = fmaxf(m_run[a], warp_max(fmaxf(sv[0], sv[1])));
+            float corr = 1.f;
+            w[0] = w[1] = 0.f;
+            if (m_new != -INFINITY) {
+                corr = expf(m_run[a] - m_new);
+                w[0] = sv[0] == -INFINITY ? 0.f : expf(sv[0] - m_new);
+                w[1] = sv[1] == -INFINITY ? 0.f : expf(sv[1] - m_new);
+            }
+            l_run[a] = l_run[a] * corr + warp_sum(w[0] + w[1]);
+            m_run[a] = m_new;
+#pragma unroll
+            for (int b = 0; b < 2; ++b) split_bf16(w[b], Ph[r * (KT + 8) + lane + 32 * b], Pl[r * (KT + 8) + lane + 32 * b]);
+            if (lane == 0) Cs[r] = corr;
+        }
+        __syncthreads();
+        {   // update of the latent columns of tiles warp, warp + 8, ...
+            const float c_lo = Cs[g], c_hi = Cs[g + 8];
+            uint32_t ah[KT / 16][4], al[KT / 16][4];
+#pragma unroll
+            for (int ks = 0; ks < KT / 16; ++ks) {
+                const __nv_bfloat16* ph = Ph + g * (KT + 8) + 16 * ks + 2 * tq4;
+                const __nv_bfloat16* pl = Pl + g * (KT + 8) + 16 * ks + 2 * tq4;
+                ah[ks][0] = *reinterpret_cast<const uint32_t*>(ph), ah[ks][1] = *reinterpret_cast<const uint32_t*>(ph + 8 * (KT + 8));
+                ah[ks][2] = *reinterpret_cast<const uint32_t*>(ph + 8), ah[ks][3] = *reinterpret_cast<const uint32_t*>(ph + 8 * (KT + 8) + 8);
+                al[ks][0] = *reinterpret_cast<const uint32_t*>(pl), al[ks][1] = *reinterpret_cast<const uint32_t*>(pl + 8 * (KT + 8));
+                al[ks][2] = *reinterpret_cast<const uint32_t*>(pl + 8), al[ks][3] = *reinterpret_cast<const uint32_t*>(pl + 8 * (KT + 8) + 8);
+            }
+#pragma unroll
+            for (int i = 0; i < NTW; ++i) {
+                const int ntile = warp + 8 * i;
+                if (ntile < n_tiles_r) {
+                    acc[i][0] *= c_lo, acc[i][1] *= c_lo, acc[i][2] *= c_hi, acc[i][3] *= c_hi;
+#pragma unroll
+                    for (int ks = 0; ks < KT / 16; ++ks) {
+                        uint32_t b0, b1;
+                        ldmatrix_x2_trans(b0, b1, Ks + (16 * ks + (lane & 15)) * LDK + 8 * ntile);
+                        mma_bf16(acc[i], ah[ks], b0, b1);
+                        mma_bf16(acc[i], al[ks], b0, b1);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (lane == 0) Cs[warp * 2] = l_run[0], Cs[warp * 2 + 1] = l_run[1], Ms[warp * 2] = m_run[0], Ms[warp * 2 + 1] = m_run[1];
+    __syncthreads();
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int r = g + 8 * hh;
+        if (row_pos[r] < 0) continue;
+        const int tq = r / HG, h = h0 + r % HG;
+        const long long row = (long long)(t0 + tq) * d.heads + h;
+        const float inv = nsplit == 1 ? 1.f / Cs[r] : 1.f;
+        float* dst = nsplit == 1 ? out_lat + row * d.R : ws_o + (row * nsplit + split) * d.R;
+#pragma unroll
+        for (int i = 0; i < NTW; ++i) {
+            const int ntile = warp + 8 * i;
+            if (ntile < n_tiles_r)
+                *reinterpret_cast<float2*>(dst + 8 * ntile + 2 * tq4) = make_float2(acc[i][2 * hh] * inv, acc[i][2 * hh + 1] * inv);
+        }
+        if (nsplit > 1 && warp == 0 && tq4 == 0) {
+            ws_ml[(row * nsplit + split) * 2] = Ms[r];
+            ws_ml[(row * nsplit + split) * 2 + 1] = Cs[r];
+        }
+    }
+}
+
 // out[row] = sum_s o_s exp(m_s - m) / sum_s l_s exp(m_s - m) over the shares of one (token, head)
 __global__ void latent_combine_kernel(const float* ws_o, const float* ws_ml, int nsplit, int R, float* out_lat) {
     const long long row = blockIdx.x;
@@ -434,6 +672,45 @@ int launch_tiled_t(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int
     dim3 grid(q_tiles, nseq * nsplit, hgs);
     const int vec = sizeof(T) == 2 && (rw & 7) == 0 && (reinterpret_cast<uintptr_t>(cache.pool) & 15) == 0;
     fn<<<grid, 256, smem, stream>>>(ix, cu_q, seq_slot, TQ, HG, nsplit, vec, q_lat, d, cache, out_lat, ws.o, ws.ml);
+    count_launch(1);
+    if (nsplit > 1) {
+        latent_combine_kernel<<<(unsigned)rows, 128, 0, stream>>>(ws.o, ws.ml, nsplit, d.R, out_lat);
+        count_launch(1);
+    }
+    ASD_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, int max_kv_len,
+               const float* q_lat, const LatentDims& d, const PagedRows& cache, float* out_lat, const AttnSplit& ws,
+               cudaStream_t stream) {
+    constexpr int QT = 16, KT = 64;
+    const int HG = d.heads < QT ? d.heads : QT;
+    int TQ = QT / HG;
+    if (TQ > max_qlen) TQ = max_qlen;
+    const int rw = d.R + d.dr, LDK = rw + 8;
+    const size_t smem = (size_t)(KT + 3 * QT) * LDK * 2 + (size_t)2 * QT * (KT + 8) * 2 + (size_t)(QT * (KT + 1) + 2 * QT) * 4;
+    const int q_tiles = (max_qlen + TQ - 1) / TQ, hgs = (d.heads + HG - 1) / HG;
+    long long keys = (long long)(d.window < max_kv_len ? d.window : max_kv_len) + TQ;
+    const int kv_tiles = (int)((keys + KT - 1) / KT);
+    int nsplit = 1;
+    const long long ctas = (long long)q_tiles * nseq * hgs, rows = (long long)ix.M * d.heads;
+    static const int two_waves = []() {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        return 2 * sms;
+    }();
+    if (ws.o && ws.ml && ctas < two_waves) {
+        nsplit = (int)(two_waves / ctas);
+        if (nsplit > kv_tiles / 2) nsplit = kv_tiles / 2;      // at least two key tiles (128 keys) per share
+        if ((long long)nsplit * rows > ws.rows) nsplit = (int)(ws.rows / rows);
+        if ((long long)nsplit * rows * d.R > ws.o_elems) nsplit = (int)(ws.o_elems / (rows * d.R));
+        if (nsplit < 1) nsplit = 1;
+        if (nsplit > 64) nsplit = 64;
+    }
+    ASD_CUDA(cudaFuncSetAttribute(latent_attn_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(q_tiles, nseq * nsplit, hgs);
+    latent_attn_mma<<<grid, 256, smem, stream>>>(ix, cu_q, seq_slot, TQ, HG, nsplit, q_lat, d, cache, out_lat, ws.o, ws.ml);
     count_launch(1);
     if (nsplit > 1) {
         latent_combine_kernel<<<(unsigned)rows, 128, 0, stream>>>(ws.o, ws.ml, nsplit, d.R, out_lat);
@@ -516,6 +793,9 @@ int launch_latent_attention(const SeqIndex& ix, const int* cu_q, const int* seq_
     const bool tiled = ws.tiled && (d.R % 4) == 0 && (rw % 4) == 0 && d.R <= 512 &&
                        (size_t)(64 * (rw + 4)) * sizeof(float) <= 200 * 1024 &&
                        (reinterpret_cast<uintptr_t>(q_lat) & 15) == 0 && (reinterpret_cast<uintptr_t>(out_lat) & 15) == 0;
+    const bool mma = ws.tiled >= 2 && !cache.f32 && (d.R % 8) == 0 && (rw % 16) == 0 && d.R <= 512 && rw <= 832 &&
+                     (reinterpret_cast<uintptr_t>(cache.pool) & 15) == 0 && (reinterpret_cast<uintptr_t>(out_lat) & 7) == 0;
+    if (mma) return launch_mma(ix, cu_q, seq_slot, nseq, max_qlen, max_kv_len, q_lat, d, cache, out_lat, ws, stream);
     if (tiled)
         return cache.f32 ? launch_tiled<float>(ix, cu_q, seq_slot, nseq, max_qlen, max_kv_len, q_lat, d, cache, out_lat, ws, stream)
                          : launch_tiled<__nv_bfloat16>(ix, cu_q, seq_slot, nseq, max_qlen, max_kv_len, q_lat, d, cache, out_lat, ws, stream);

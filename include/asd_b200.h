@@ -291,8 +291,9 @@ ASD_API int asd_mezilix_set_cache(asd_mezilix_engine_t* e, void* pool, int num_p
                                   int max_seqs, int max_pages_per_seq, int32_t* token_ring, float* shift_ring);
 /* options: "tc_linear" (1, default: bf16 projections whose shape the tcgen05 kernels accept run on them; 0: CUDA-core
  * kernel everywhere), "tc_min_rows" (token count from which dense projections use the tensor-bound CTA-pair GEMM, default
- * 257; 0 = never), "attn_tiled" (1, default: register-tiled attention kernel with key-range shares where the latent
- * size allows; 0: one warp per (token, head)), "profile" (1: CUDA events around every launch, read with asd_mezilix_profile_read) */
+ * 257; 0 = never), "attn_tiled" (2, default: attention of bf16 cache rows on the tensor cores with fp32 operands as two
+ * bf16 terms, else as 1; 1: register-tiled fp32 kernel with key-range shares where the latent size allows; 0: one warp
+ * per (token, head)), "profile" (1: CUDA events around every launch, read with asd_mezilix_profile_read) */
 ASD_API int asd_mezilix_set_option(asd_mezilix_engine_t* e, const char* name, int value);
 /* Same contract as asd_engine_forward (M <= max_tokens).  layer_out (optional, fp32 [n_layers][M][width]) receives
  * the stream that leaves every layer. */

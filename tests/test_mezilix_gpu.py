@@ -220,7 +220,7 @@ def test_pages_and_slots_freed_and_used_again():
 
 def standout_model(window, n_layers=1):
     """sharp softmax (large scale) and weights that spread the scores: single keys carry most of the weight"""
-    cfg = config([layer(heads=2, dim=16, rot_dim=8, vdim=16, kv_rank=32, window=window, scale=3.0, experts=0)
+    cfg = config([layer(heads=2, dim=16, rot_dim=8, vdim=16, kv_rank=40, window=window, scale=3.0, experts=0)
                   for _ in range(n_layers)])
     return cfg, O.random_model(cfg, seed=19, scale=2.0)
 
@@ -244,8 +244,9 @@ def plant_pair(cfg, w, key_tok, query_tok, boost=600.0):
     w["l0.mix.q"] = q.reshape(H * (dn + dr), -1).to(torch.bfloat16)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
 @pytest.mark.parametrize("window,page_size", [(9, 16), (16, 16), (33, 4), (300, 16), (257, 8), (1000, 16)])
-def test_window_edges_with_standout_keys(window, page_size):
+def test_window_edges_with_standout_keys(window, page_size, dtype):
     """a key that outweighs everything else sits exactly window - 1 positions back (the last one visible) for one
     query and exactly window positions back (the first one hidden) for another, in a prompt and while decoding, far
     away among hundreds of keys and on the first and last row of a page"""
@@ -269,17 +270,22 @@ def test_window_edges_with_standout_keys(window, page_size):
         c2["layers"][0]["mixer"]["mask"]["size"] = wrong
         other, _ = O.forward(c2, w, ids)
         for p in places:
-            assert rel_err(other[p:p + 1].float(), ref[p:p + 1])[1] > 0.3
+            assert rel_err(other[p:p + 1].float(), ref[p:p + 1])[1] > 1.0
     first_q = min(at_in + at_out)
     for cuts in ([n], [first_q - 1, 2, 1, 1, 37, 2, 1, 1], [first_q - 3] + [1] * (n - first_q + 3), [2] * (n // 2)):
-        eng = make_engine(cfg, w, max_tokens=512, page_size=page_size, max_seq_len=1280)
+        eng = make_engine(cfg, w, max_tokens=512, page_size=page_size, max_seq_len=1280, dtype=dtype)
         slot = eng.open_sequence()
         got = feed(eng, slot, ids, cuts)
-        # planted scores are about 600, where one fp32 ulp is 6e-5: the weights carry that rounding, an off-by-one 0.3
-        assert rel_err(got, ref)[1] < 1e-3
+        # planted scores are about 600, where one fp32 ulp is 6e-5: the weights carry that rounding, an off-by-one 1.0.
+        # The bf16 engine (tensor-core attention: a latent row of 48 elements) is held to its own roundings.
+        tol = 1e-3 if dtype == torch.float32 else 0.3
+        if dtype == torch.float32:
+            assert rel_err(got, ref)[1] < tol
+        else:
+            assert rel_err(got, ref)[0] < 6e-2
         for p in at_in + at_out:
-            assert rel_err(got[p:p + 1], ref[p:p + 1])[1] < 1e-3
-        eng.close()
+            assert rel_err(got[p:p + 1], ref[p:p + 1])[1] < tol
+        close(eng)
 
 
 def test_both_attention_kernels_agree_with_the_oracle():
@@ -297,6 +303,26 @@ def test_both_attention_kernels_agree_with_the_oracle():
             got = feed(eng, slot, ids, [3, 830, 1, 1, 1, 2, 40, 1, 1])
             assert rel_err(got, ref)[1] < 3e-4, (heads, tiled)
             close(eng)
+
+
+def test_tensor_core_attention_keeps_fp32_scores():
+    """bf16 engine: attention on the tensor cores (the query as three bf16 terms, the weights as two) against the fp32
+    CUDA-core kernels on the same cache; a sharp softmax (large scale) would expose scores kept to bf16 only"""
+    cfg = config([layer(heads=5, dim=16, rot_dim=16, vdim=16, kv_rank=48, window=500, scale=2.0, experts=0)], width=64)
+    w = O.random_model(cfg, seed=45, scale=2.0)
+    ids = tokens(700, 96, 46)
+    outs = []
+    for mode in (2, 1, 0):
+        eng = make_engine(cfg, w, dtype=torch.bfloat16, max_tokens=1024, max_seq_len=1024)
+        eng.set_option("attn_tiled", mode)
+        outs.append(feed(eng, eng.open_sequence(), ids, [3, 600, 1, 1, 1, 2, 40, 1, 1]).cpu())
+        close(eng)
+    # both fp32 kernels form the same sums; the tensor-core kernel may round elsewhere, and in a bf16 engine every later
+    # bf16 rounding amplifies that, so it is held to the oracle: no further from it than the fp32 kernels are
+    assert rel_err(outs[1], outs[2].double())[1] < 2e-4
+    ref, _ = O.forward(cfg, w, ids)
+    e_tc, e_fp32 = rel_err(outs[0], ref)[0], rel_err(outs[1], ref)[0]
+    assert e_fp32 < 4e-2 and e_tc < 1.1 * e_fp32 + 1e-4, (e_tc, e_fp32)
 
 
 def test_long_decoding_past_window_ring_and_pages():
