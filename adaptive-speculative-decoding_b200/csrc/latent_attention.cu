@@ -403,10 +403,11 @@ __device__ __forceinline__ void split_bf16(float x, __nv_bfloat16& hi, __nv_bflo
     lo = __float2bfloat16(x - __bfloat162float(hi));
 }
 
+template <int MT>   // 16-row tiles per CTA: 1 (few rows: decode) or 2 (prompts: a key tile serves twice the rows)
 __global__ void __launch_bounds__(256, 1) latent_attn_mma(SeqIndex ix, const int* cu_q, const int* seq_slot, int TQ, int HG,
                                                           int nsplit, const float* q_lat, LatentDims d, PagedRows cache,
                                                           float* out_lat, float* ws_o, float* ws_ml) {
-    constexpr int QT = 16, KT = 64, NTW = 8;                  // NTW: 8-wide latent tiles per warp (R <= 512)
+    constexpr int QT = 16 * MT, KT = 64, NTW = 8, RW = 2 * MT;                  // NTW: 8-wide latent tiles per warp (R <= 512)
     extern __shared__ __align__(16) uint8_t smem_b[];
     const int rw = d.R + d.dr, LDK = rw + 8;                  // bf16 elements per staged row (16-byte multiple)
     __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_b);          // [KT][LDK]
@@ -467,10 +468,14 @@ __global__ void __launch_bounds__(256, 1) latent_attn_mma(SeqIndex ix, const int
             }
         }
     }
-    float acc[NTW][4];
+    float acc[MT][NTW][4];
 #pragma unroll
-    for (int i = 0; i < NTW; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < NTW; ++i) acc[mt][i][0] = acc[mt][i][1] = acc[mt][i][2] = acc[mt][i][3] = 0.f;
+    float m_run[RW], l_run[RW];
+#pragma unroll
+    for (int i = 0; i < RW; ++i) m_run[i] = -INFINITY, l_run[i] = 0.f;
     const __nv_bfloat16* pool = (const __nv_bfloat16*)cache.pool;
     constexpr int MAXCH = 26;                                 // 64 rows x (rw / 8) chunks over 256 threads, rw <= 832
     uint4 pre[MAXCH];
@@ -513,36 +518,45 @@ __global__ void __launch_bounds__(256, 1) latent_attn_mma(SeqIndex ix, const int
         if (t + 1 < te) fetch(t + 1);
         locate(t + 2);
         __syncthreads();
-        {   // scores of keys 8 warp .. 8 warp + 7 for all 16 rows
-            float st[3][4];                  // one accumulator per term: three independent MMA chains
+        {   // scores of keys 8 warp .. 8 warp + 7 for all rows: a key fragment serves 3 MT products
+            float st[MT][3][4];              // one accumulator per row tile and term: independent MMA chains
 #pragma unroll
-            for (int u = 0; u < 3; ++u) st[u][0] = st[u][1] = st[u][2] = st[u][3] = 0.f;
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int u = 0; u < 3; ++u) st[mt][u][0] = st[mt][u][1] = st[mt][u][2] = st[mt][u][3] = 0.f;
             const __nv_bfloat16* kb = Ks + (warp * 8 + g) * LDK + 2 * tq4;
             const __nv_bfloat16* qt[3] = {Qh + g * LDK + 2 * tq4, Qm + g * LDK + 2 * tq4, Ql + g * LDK + 2 * tq4};
 #pragma unroll 2
             for (int k0 = 0; k0 < rw; k0 += 16) {
                 const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + k0), b1 = *reinterpret_cast<const uint32_t*>(kb + k0 + 8);
 #pragma unroll
-                for (int u = 0; u < 3; ++u) {
-                    uint32_t a[4];
-                    a[0] = *reinterpret_cast<const uint32_t*>(qt[u] + k0);
-                    a[1] = *reinterpret_cast<const uint32_t*>(qt[u] + 8 * LDK + k0);
-                    a[2] = *reinterpret_cast<const uint32_t*>(qt[u] + k0 + 8);
-                    a[3] = *reinterpret_cast<const uint32_t*>(qt[u] + 8 * LDK + k0 + 8);
-                    mma_bf16(st[u], a, b0, b1);
-                }
-            }
-            float sc[4];
+                for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) sc[e] = st[0][e] + (st[1][e] + st[2][e]);
+                    for (int u = 0; u < 3; ++u) {
+                        const __nv_bfloat16* q = qt[u] + mt * 16 * LDK + k0;
+                        uint32_t a[4];
+                        a[0] = *reinterpret_cast<const uint32_t*>(q);
+                        a[1] = *reinterpret_cast<const uint32_t*>(q + 8 * LDK);
+                        a[2] = *reinterpret_cast<const uint32_t*>(q + 8);
+                        a[3] = *reinterpret_cast<const uint32_t*>(q + 8 * LDK + 8);
+                        mma_bf16(st[mt][u], a, b0, b1);
+                    }
+            }
             const int col = warp * 8 + 2 * tq4;
-            Ss[g * (KT + 1) + col] = sc[0], Ss[g * (KT + 1) + col + 1] = sc[1];
-            Ss[(g + 8) * (KT + 1) + col] = sc[2], Ss[(g + 8) * (KT + 1) + col + 1] = sc[3];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                float sc[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[e] = st[mt][0][e] + (st[mt][1][e] + st[mt][2][e]);
+                float* dst = Ss + (mt * 16 + g) * (KT + 1) + col;
+                dst[0] = sc[0], dst[1] = sc[1];
+                dst[8 * (KT + 1)] = sc[2], dst[8 * (KT + 1) + 1] = sc[3];
+            }
         }
         __syncthreads();
 #pragma unroll
-        for (int a = 0; a < 2; ++a) {        // running softmax of rows 2 warp, 2 warp + 1; lane = keys lane, lane + 32
-            const int r = warp * 2 + a, p = row_pos[r];
+        for (int a = 0; a < RW; ++a) {       // running softmax of rows RW warp ..; lane = keys lane, lane + 32
+            const int r = warp * RW + a, p = row_pos[r];
             float sv[2], w[2];
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
@@ -565,40 +579,51 @@ __global__ void __launch_bounds__(256, 1) latent_attn_mma(SeqIndex ix, const int
             if (lane == 0) Cs[r] = corr;
         }
         __syncthreads();
-        {   // update of the latent columns of tiles warp, warp + 8, ...
-            const float c_lo = Cs[g], c_hi = Cs[g + 8];
-            uint32_t ah[KT / 16][4], al[KT / 16][4];
+        {   // update of the latent columns of tiles warp, warp + 8, ...: a key fragment serves 2 MT products
 #pragma unroll
-            for (int ks = 0; ks < KT / 16; ++ks) {
-                const __nv_bfloat16* ph = Ph + g * (KT + 8) + 16 * ks + 2 * tq4;
-                const __nv_bfloat16* pl = Pl + g * (KT + 8) + 16 * ks + 2 * tq4;
-                ah[ks][0] = *reinterpret_cast<const uint32_t*>(ph), ah[ks][1] = *reinterpret_cast<const uint32_t*>(ph + 8 * (KT + 8));
-                ah[ks][2] = *reinterpret_cast<const uint32_t*>(ph + 8), ah[ks][3] = *reinterpret_cast<const uint32_t*>(ph + 8 * (KT + 8) + 8);
-                al[ks][0] = *reinterpret_cast<const uint32_t*>(pl), al[ks][1] = *reinterpret_cast<const uint32_t*>(pl + 8 * (KT + 8));
-                al[ks][2] = *reinterpret_cast<const uint32_t*>(pl + 8), al[ks][3] = *reinterpret_cast<const uint32_t*>(pl + 8 * (KT + 8) + 8);
+            for (int mt = 0; mt < MT; ++mt) {
+                const float c_lo = Cs[mt * 16 + g], c_hi = Cs[mt * 16 + g + 8];
+#pragma unroll
+                for (int i = 0; i < NTW; ++i)
+                    acc[mt][i][0] *= c_lo, acc[mt][i][1] *= c_lo, acc[mt][i][2] *= c_hi, acc[mt][i][3] *= c_hi;
             }
 #pragma unroll
-            for (int i = 0; i < NTW; ++i) {
-                const int ntile = warp + 8 * i;
-                if (ntile < n_tiles_r) {
-                    acc[i][0] *= c_lo, acc[i][1] *= c_lo, acc[i][2] *= c_hi, acc[i][3] *= c_hi;
+            for (int ks = 0; ks < KT / 16; ++ks) {
+                uint32_t ah[MT][4], al[MT][4];
 #pragma unroll
-                    for (int ks = 0; ks < KT / 16; ++ks) {
+                for (int mt = 0; mt < MT; ++mt) {
+                    const __nv_bfloat16* ph = Ph + (mt * 16 + g) * (KT + 8) + 16 * ks + 2 * tq4;
+                    const __nv_bfloat16* pl = Pl + (mt * 16 + g) * (KT + 8) + 16 * ks + 2 * tq4;
+                    ah[mt][0] = *reinterpret_cast<const uint32_t*>(ph), ah[mt][1] = *reinterpret_cast<const uint32_t*>(ph + 8 * (KT + 8));
+                    ah[mt][2] = *reinterpret_cast<const uint32_t*>(ph + 8), ah[mt][3] = *reinterpret_cast<const uint32_t*>(ph + 8 * (KT + 8) + 8);
+                    al[mt][0] = *reinterpret_cast<const uint32_t*>(pl), al[mt][1] = *reinterpret_cast<const uint32_t*>(pl + 8 * (KT + 8));
+                    al[mt][2] = *reinterpret_cast<const uint32_t*>(pl + 8), al[mt][3] = *reinterpret_cast<const uint32_t*>(pl + 8 * (KT + 8) + 8);
+                }
+#pragma unroll
+                for (int i = 0; i < NTW; ++i) {
+                    const int ntile = warp + 8 * i;
+                    if (ntile < n_tiles_r) {
                         uint32_t b0, b1;
                         ldmatrix_x2_trans(b0, b1, Ks + (16 * ks + (lane & 15)) * LDK + 8 * ntile);
-                        mma_bf16(acc[i], ah[ks], b0, b1);
-                        mma_bf16(acc[i], al[ks], b0, b1);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            mma_bf16(acc[mt][i], ah[mt], b0, b1);
+                            mma_bf16(acc[mt][i], al[mt], b0, b1);
+                        }
                     }
                 }
             }
         }
     }
     __syncthreads();
-    if (lane == 0) Cs[warp * 2] = l_run[0], Cs[warp * 2 + 1] = l_run[1], Ms[warp * 2] = m_run[0], Ms[warp * 2 + 1] = m_run[1];
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < RW; ++i) Cs[warp * RW + i] = l_run[i], Ms[warp * RW + i] = m_run[i];
+    }
     __syncthreads();
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-        const int r = g + 8 * hh;
+    for (int mh = 0; mh < 2 * MT; ++mh) {
+        const int mt = mh >> 1, hh = mh & 1, r = mt * 16 + g + 8 * hh;
         if (row_pos[r] < 0) continue;
         const int tq = r / HG, h = h0 + r % HG;
         const long long row = (long long)(t0 + tq) * d.heads + h;
@@ -608,7 +633,8 @@ __global__ void __launch_bounds__(256, 1) latent_attn_mma(SeqIndex ix, const int
         for (int i = 0; i < NTW; ++i) {
             const int ntile = warp + 8 * i;
             if (ntile < n_tiles_r)
-                *reinterpret_cast<float2*>(dst + 8 * ntile + 2 * tq4) = make_float2(acc[i][2 * hh] * inv, acc[i][2 * hh + 1] * inv);
+                *reinterpret_cast<float2*>(dst + 8 * ntile + 2 * tq4) =
+                    make_float2(acc[mt][i][2 * hh] * inv, acc[mt][i][2 * hh + 1] * inv);
         }
         if (nsplit > 1 && warp == 0 && tq4 == 0) {
             ws_ml[(row * nsplit + split) * 2] = Ms[r];
@@ -681,10 +707,11 @@ int launch_tiled_t(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int
     return 0;
 }
 
-int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, int max_kv_len,
-               const float* q_lat, const LatentDims& d, const PagedRows& cache, float* out_lat, const AttnSplit& ws,
-               cudaStream_t stream) {
-    constexpr int QT = 16, KT = 64;
+template <int MT>
+int launch_mma_t(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, int max_kv_len,
+                 const float* q_lat, const LatentDims& d, const PagedRows& cache, float* out_lat, const AttnSplit& ws,
+                 cudaStream_t stream) {
+    constexpr int QT = 16 * MT, KT = 64;
     const int HG = d.heads < QT ? d.heads : QT;
     int TQ = QT / HG;
     if (TQ > max_qlen) TQ = max_qlen;
@@ -708,9 +735,9 @@ int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nse
         if (nsplit < 1) nsplit = 1;
         if (nsplit > 64) nsplit = 64;
     }
-    ASD_CUDA(cudaFuncSetAttribute(latent_attn_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    ASD_CUDA(cudaFuncSetAttribute(latent_attn_mma<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(q_tiles, nseq * nsplit, hgs);
-    latent_attn_mma<<<grid, 256, smem, stream>>>(ix, cu_q, seq_slot, TQ, HG, nsplit, q_lat, d, cache, out_lat, ws.o, ws.ml);
+    latent_attn_mma<MT><<<grid, 256, smem, stream>>>(ix, cu_q, seq_slot, TQ, HG, nsplit, q_lat, d, cache, out_lat, ws.o, ws.ml);
     count_launch(1);
     if (nsplit > 1) {
         latent_combine_kernel<<<(unsigned)rows, 128, 0, stream>>>(ws.o, ws.ml, nsplit, d.R, out_lat);
@@ -718,6 +745,17 @@ int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nse
     }
     ASD_CUDA(cudaGetLastError());
     return 0;
+}
+
+int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, int max_kv_len,
+               const float* q_lat, const LatentDims& d, const PagedRows& cache, float* out_lat, const AttnSplit& ws,
+               cudaStream_t stream) {
+    const long long need = (long long)(d.heads < 32 ? d.heads : 32) * (max_qlen < 32 ? max_qlen : 32);
+    const int LDK = d.R + d.dr + 8;
+    const size_t smem2 = (size_t)(64 + 3 * 32) * LDK * 2 + (size_t)2 * 32 * 72 * 2 + (size_t)(32 * 65 + 64) * 4;
+    if (need >= 32 && smem2 <= 220 * 1024)
+        return launch_mma_t<2>(ix, cu_q, seq_slot, nseq, max_qlen, max_kv_len, q_lat, d, cache, out_lat, ws, stream);
+    return launch_mma_t<1>(ix, cu_q, seq_slot, nseq, max_qlen, max_kv_len, q_lat, d, cache, out_lat, ws, stream);
 }
 
 template <typename T>
