@@ -78,6 +78,11 @@ struct LayerClose {
     float* x_next;
     float* hn;
     int M, D;
+    // optional: before hn is overwritten, the rows that own a ring entry store their hn (this layer's normed input) as
+    // the carried state of the token shift (what launch_commit_shift_state does, without its launch)
+    const SeqIndex* ix = nullptr;
+    float* state_ring = nullptr;
+    int ring = 0;
 };
 int launch_layer_close(const LayerClose& L, cudaStream_t stream);
 // dst[r] = src[rows[r]] converted to the engine's element type (rows == nullptr: identity)

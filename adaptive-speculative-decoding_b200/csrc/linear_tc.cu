@@ -7,8 +7,8 @@
 //     128 rows) the B operand (N = MT), one accumulator [128 lanes x MT columns] in TMEM;
 //   * operands go global -> registers -> shared memory in the K-major 128-byte-swizzled layout the MMA descriptors
 //     expect (what TMA would have produced): 16-byte chunk c of row r lands at (r / 8) * 1024 + (r % 8) * 128 +
-//     ((c ^ (r % 8)) * 16).  All 256 threads load; the registers of k-block i + 1 are in flight while k-block i is
-//     stored, fenced to the async proxy and issued;
+//     ((c ^ (r % 8)) * 16).  All 256 threads load; the registers of k-blocks i + 1 and i + 2 are in flight while k-block
+//     i is stored, fenced to the async proxy and issued;
 //   * three shared-memory stages; tcgen05.commit frees a stage when the MMAs that read it have retired;
 //   * epilogue: the eight warps read their TMEM lane quarter 16 token columns at a time; lane = weight row, so the 32
 //     lanes of a warp write 32 consecutive outputs of one token.
@@ -108,30 +108,30 @@ __global__ void __launch_bounds__(kThreads) tc_linear_kernel(SimtLinear L, int M
         }
     }
     const int nkb = (L.K + kBK - 1) / kBK;
-    uint4 wr[4], xr[4];
+    // two register sets: the loads of k-blocks i + 1 and i + 2 are in flight while k-block i is stored and issued
+    uint4 wr[2][4], xr[2][4];
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
-    auto fetch = [&](int kb) {
+    auto fetch = [&](int kb, uint4 (&w4)[4], uint4 (&x4)[4]) {
         const int k = kb * kBK + c * 8;
         const bool in = k < L.K;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            wr[i] = (in && wrow[i]) ? load8(wrow[i] + k) : zero4;
-            xr[i] = (in && xrow[i]) ? load8(xrow[i] + k) : zero4;
+            w4[i] = (in && wrow[i]) ? load8(wrow[i] + k) : zero4;
+            x4[i] = (in && xrow[i]) ? load8(xrow[i] + k) : zero4;
         }
     };
     const uint32_t idesc = umma_idesc_bf16(kRowsW, MT);
-    fetch(0);
-    for (int kb = 0; kb < nkb; ++kb) {
+    auto step = [&](int kb, uint4 (&w4)[4], uint4 (&x4)[4]) {
         const int s = kb % kStages, round = kb / kStages;
         if (round > 0) wait_bounded(&empty_bar[s], (round - 1) & 1, &failed, err);
         uint8_t* st = smem + (size_t)s * stage_bytes;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int r = r0 + 32 * i;
-            *reinterpret_cast<uint4*>(st + swz(r, c)) = wr[i];
-            if (r < MT) *reinterpret_cast<uint4*>(st + kWBytes + swz(r, c)) = xr[i];
+            *reinterpret_cast<uint4*>(st + swz(r, c)) = w4[i];
+            if (r < MT) *reinterpret_cast<uint4*>(st + kWBytes + swz(r, c)) = x4[i];
         }
-        if (kb + 1 < nkb) fetch(kb + 1);
+        if (kb + 2 < nkb) fetch(kb + 2, w4, x4);
         fence_proxy_async_smem();
         __syncthreads();
         if (tid == 0) {
@@ -143,6 +143,12 @@ __global__ void __launch_bounds__(kThreads) tc_linear_kernel(SimtLinear L, int M
             umma_commit(&empty_bar[s]);
             if (kb == nkb - 1) umma_commit(&acc_bar);
         }
+    };
+    fetch(0, wr[0], xr[0]);
+    if (nkb > 1) fetch(1, wr[1], xr[1]);
+    for (int kb = 0; kb < nkb; kb += 2) {
+        step(kb, wr[0], xr[0]);
+        if (kb + 1 < nkb) step(kb + 1, wr[1], xr[1]);
     }
     const bool ok = wait_bounded(&acc_bar, 0, &failed, err);
     tc_fence_after();

@@ -136,7 +136,6 @@ static int forward(MzEngine* e, const int* tokens, const int* positions, const i
         {
             MZ_PROF(MZ_GLUE);
             if (launch_token_shift(ix, e->hn, ring_l, ring, ly.shift, f32, e->h, e->hs, f32, D, s)) return -1;
-            if (launch_commit_shift_state(ix, e->hn, ring_l, ring, D, s)) return -1;
         }
         {   // queries | latent | rotated key in one projection
             MZ_PROF(MZ_DENSE);
@@ -210,6 +209,7 @@ static int forward(MzEngine* e, const int* tokens, const int* positions, const i
         C.g_next = l + 1 < nl ? e->layers[l + 1].gain : e->final_gain;
         C.wf32 = f32, C.eps = e->c.eps;
         C.x_next = e->xavg, C.hn = e->hn, C.M = M, C.D = D;
+        C.ix = &ix, C.state_ring = ring_l, C.ring = ring;     // this layer's normed input becomes the shift's carried state
         if (launch_layer_close(C, s)) return -1;
         if (layer_out)
             ASD_CUDA(cudaMemcpyAsync(layer_out + (size_t)l * M * D, e->xavg, sizeof(float) * M * D,

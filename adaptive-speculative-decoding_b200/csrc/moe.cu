@@ -89,6 +89,80 @@ __global__ void moe_route_kernel(const float* logits, const void* x, int xf32, c
     }
 }
 
+// Few tokens (M * top <= 4096): choice, group sizes, offsets and scatter in ONE CTA with shared-memory counters, so that a
+// decode step spends two launches on routing (logits, then this) instead of five.
+__global__ void __launch_bounds__(256) moe_route_small_kernel(const float* logits, int M, int E, int top, int* expert_of,
+                                                              float* gate, int* group_off, int* sorted_tok, int* slot_of) {
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    int* cnt = reinterpret_cast<int*>(sm + (size_t)nw * E);     // [E] group sizes, then fill counters
+    int* off = cnt + E;                                          // [E + 1]
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    float* pr = sm + (size_t)warp * E;
+    for (int m = warp; m < M; m += nw) {
+        const float* z = logits + (long long)m * E;
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        float s = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float v = expf(z[e] - mx);
+            pr[e] = v;
+            s += v;
+        }
+        s = warp_sum(s);
+        const float inv = 1.f / s;
+        __syncwarp();
+        for (int k = 0; k < top; ++k) {
+            float best = -1.f;
+            int bi = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float v = pr[e];
+                if (v > best) {
+                    best = v;
+                    bi = e;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ob > best || (ob == best && oi < bi)) {
+                    best = ob;
+                    bi = oi;
+                }
+            }
+            if (lane == 0) {
+                expert_of[(long long)m * top + k] = bi;
+                gate[(long long)m * top + k] = best * inv;
+                atomicAdd(&cnt[bi], 1);
+                pr[bi] = -2.f;
+            }
+            __syncwarp();
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0;
+        for (int e = 0; e < E; ++e) {
+            off[e] = o;
+            group_off[e] = o;
+            o += cnt[e];
+            cnt[e] = 0;
+        }
+        off[E] = o;
+        group_off[E] = o;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < M * top; i += blockDim.x) {
+        const int e = expert_of[i];
+        const int slot = off[e] + atomicAdd(&cnt[e], 1);
+        sorted_tok[slot] = i / top;
+        slot_of[i] = slot;
+    }
+}
+
 // router logits, one CTA per token: z[m][e] = sum_d x[m][d] * wr[e][d] in fp32.  Thread t sums d = t, t + 128, ... in
 // increasing order, then the fixed warp tree and the warps in index order: a token's logits do not depend on the batch.
 __global__ void __launch_bounds__(128) moe_logits_kernel(const void* x, int xf32, const void* wr, int wf32, int D, int E,
@@ -148,6 +222,14 @@ int launch_moe_route(const float* logits, const MoeRouterInput* in, int M, int E
     if (E <= 0 || top <= 0 || top > E) return set_error("moe: need 0 < top <= experts (top %d, experts %d)", top, E);
     if ((size_t)E * 8 * sizeof(float) > 48 * 1024) return set_error("moe: more than 1536 experts");
     if (!logits && !in) return set_error("moe: neither logits nor router inputs");
+    if (in && in->logits_out && (long long)M * top <= 4096 && (size_t)(8 * E + 2 * E + 1) * 4 <= 48 * 1024) {
+        moe_logits_kernel<<<M, 128, 0, stream>>>(in->x, in->x_f32, in->w, in->w_f32, in->D, E, in->logits_out);
+        moe_route_small_kernel<<<1, 256, (size_t)(8 * E + 2 * E + 1) * sizeof(float), stream>>>(
+            in->logits_out, M, E, top, expert_of, gate, group_off, sorted_tok, slot_of);
+        count_launch(2);
+        ASD_CUDA(cudaGetLastError());
+        return 0;
+    }
     ASD_CUDA(cudaMemsetAsync(counters, 0, sizeof(int) * E, stream));
     if (in && in->logits_out) {          // a CTA per token for the logits: few tokens still spread over the GPU
         moe_logits_kernel<<<M, 128, 0, stream>>>(in->x, in->x_f32, in->w, in->w_f32, in->D, E, in->logits_out);

@@ -76,10 +76,14 @@ __global__ void commit_shift_kernel(SeqIndex ix, const float* hn, float* state, 
     for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = hn[(long long)m * D + d];
 }
 
-__global__ void layer_close_kernel(LayerClose L) {
+__global__ void layer_close_kernel(LayerClose L, SeqIndex ix) {
     __shared__ float red[33];
     const int m = blockIdx.x, D = L.D;
     const long long base = (long long)m * D;
+    if (L.state_ring && owns_ring_entry(ix, m, L.ring)) {
+        float* dst = L.state_ring + ((long long)ix.token_slot[m] * L.ring + ix.positions[m] % L.ring) * D;
+        for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = L.hn[base + d];
+    }
     float* xnew = L.stack + (size_t)(L.layer + 1) * L.stack_stride + base;
     float ss = 0.f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
@@ -153,7 +157,8 @@ int launch_commit_shift_state(const SeqIndex& ix, const float* hn, float* state_
 
 int launch_layer_close(const LayerClose& L, cudaStream_t stream) {
     if (L.M <= 0) return 0;
-    layer_close_kernel<<<L.M, row_threads(L.D), 0, stream>>>(L);
+    if (L.state_ring && (!L.ix || L.ring <= 0)) return set_error("layer_close: the carried state needs the batch index and a ring");
+    layer_close_kernel<<<L.M, row_threads(L.D), 0, stream>>>(L, L.ix ? *L.ix : SeqIndex{nullptr, nullptr, nullptr, 0});
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
     return 0;
