@@ -398,6 +398,18 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& b0, uint32_t& b1, co
     const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
 }
+// A fragment (16 rows x 16 k) of a row-major bf16 tile: lane l names row l % 16 at column 8 * (l / 16)
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&a)[4], const void* smem_row) {
+    const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                 : "r"(addr));
+}
+// B fragment (16 k x 8 n) of a tile stored [n][k]: lanes 0-7 name rows n at column 0, lanes 8-15 at column 8
+__device__ __forceinline__ void ldmatrix_x2(uint32_t& b0, uint32_t& b1, const void* smem_row) {
+    const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+}
 __device__ __forceinline__ void split_bf16(float x, __nv_bfloat16& hi, __nv_bfloat16& lo) {
     hi = __float2bfloat16(x);
     lo = __float2bfloat16(x - __bfloat162float(hi));
@@ -477,17 +489,19 @@ __global__ void __launch_bounds__(256, 1) latent_attn_mma(SeqIndex ix, const int
 #pragma unroll
     for (int i = 0; i < RW; ++i) m_run[i] = -INFINITY, l_run[i] = 0.f;
     const __nv_bfloat16* pool = (const __nv_bfloat16*)cache.pool;
-    constexpr int MAXCH = 26;                                 // 64 rows x (rw / 8) chunks over 256 threads, rw <= 832
-    uint4 pre[MAXCH];
-    const int cpr = rw >> 3, nch = KT * cpr;
+    // key rows of a tile -> registers: warp w takes rows 8 w .. 8 w + 7, lane l the 16-byte chunks l, l + 32, l + 64 of
+    // each (a warp reads 512 contiguous bytes; no index arithmetic beyond adds)
+    constexpr int CPL = 3;                                    // chunks per lane and row: row length <= 768 elements
+    uint4 pre[8][CPL];
+    const int cpr = rw >> 3;
     auto fetch = [&](int t) {
 #pragma unroll
-        for (int i = 0; i < MAXCH; ++i) {
-            const int idx = tid + 256 * i;
-            if (idx < nch) {
-                const int r = idx / cpr, c = idx - r * cpr;
-                const long long row = key_row[t & 1][r];
-                pre[i] = row >= 0 ? *reinterpret_cast<const uint4*>(pool + row * rw + 8 * c) : make_uint4(0, 0, 0, 0);
+        for (int j = 0; j < 8; ++j) {
+            const long long row = key_row[t & 1][warp * 8 + j];
+#pragma unroll
+            for (int u = 0; u < CPL; ++u) {
+                const int c = lane + 32 * u;
+                pre[j][u] = (row >= 0 && c < cpr) ? *reinterpret_cast<const uint4*>(pool + row * rw + 8 * c) : make_uint4(0, 0, 0, 0);
             }
         }
     };
@@ -508,13 +522,12 @@ __global__ void __launch_bounds__(256, 1) latent_attn_mma(SeqIndex ix, const int
         const int j0 = j_lo + t * KT;
         __syncthreads();
 #pragma unroll
-        for (int i = 0; i < MAXCH; ++i) {
-            const int idx = tid + 256 * i;
-            if (idx < nch) {
-                const int r = idx / cpr, c = idx - r * cpr;
-                *reinterpret_cast<uint4*>(Ks + r * LDK + 8 * c) = pre[i];
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int u = 0; u < CPL; ++u) {
+                const int c = lane + 32 * u;
+                if (c < cpr) *reinterpret_cast<uint4*>(Ks + (warp * 8 + j) * LDK + 8 * c) = pre[j][u];
             }
-        }
         if (t + 1 < te) fetch(t + 1);
         locate(t + 2);
         __syncthreads();
@@ -524,21 +537,19 @@ __global__ void __launch_bounds__(256, 1) latent_attn_mma(SeqIndex ix, const int
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                 for (int u = 0; u < 3; ++u) st[mt][u][0] = st[mt][u][1] = st[mt][u][2] = st[mt][u][3] = 0.f;
-            const __nv_bfloat16* kb = Ks + (warp * 8 + g) * LDK + 2 * tq4;
-            const __nv_bfloat16* qt[3] = {Qh + g * LDK + 2 * tq4, Qm + g * LDK + 2 * tq4, Ql + g * LDK + 2 * tq4};
+            const __nv_bfloat16* kb = Ks + (warp * 8 + (lane & 7)) * LDK + 8 * ((lane >> 3) & 1);
+            const int qoff = (lane & 15) * LDK + 8 * (lane >> 4);
+            const __nv_bfloat16* qt[3] = {Qh + qoff, Qm + qoff, Ql + qoff};
 #pragma unroll 2
             for (int k0 = 0; k0 < rw; k0 += 16) {
-                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + k0), b1 = *reinterpret_cast<const uint32_t*>(kb + k0 + 8);
+                uint32_t b0, b1;
+                ldmatrix_x2(b0, b1, kb + k0);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                     for (int u = 0; u < 3; ++u) {
-                        const __nv_bfloat16* q = qt[u] + mt * 16 * LDK + k0;
                         uint32_t a[4];
-                        a[0] = *reinterpret_cast<const uint32_t*>(q);
-                        a[1] = *reinterpret_cast<const uint32_t*>(q + 8 * LDK);
-                        a[2] = *reinterpret_cast<const uint32_t*>(q + 8);
-                        a[3] = *reinterpret_cast<const uint32_t*>(q + 8 * LDK + 8);
+                        ldmatrix_x4(a, qt[u] + mt * 16 * LDK + k0);
                         mma_bf16(st[mt][u], a, b0, b1);
                     }
             }
@@ -592,12 +603,9 @@ __global__ void __launch_bounds__(256, 1) latent_attn_mma(SeqIndex ix, const int
                 uint32_t ah[MT][4], al[MT][4];
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    const __nv_bfloat16* ph = Ph + (mt * 16 + g) * (KT + 8) + 16 * ks + 2 * tq4;
-                    const __nv_bfloat16* pl = Pl + (mt * 16 + g) * (KT + 8) + 16 * ks + 2 * tq4;
-                    ah[mt][0] = *reinterpret_cast<const uint32_t*>(ph), ah[mt][1] = *reinterpret_cast<const uint32_t*>(ph + 8 * (KT + 8));
-                    ah[mt][2] = *reinterpret_cast<const uint32_t*>(ph + 8), ah[mt][3] = *reinterpret_cast<const uint32_t*>(ph + 8 * (KT + 8) + 8);
-                    al[mt][0] = *reinterpret_cast<const uint32_t*>(pl), al[mt][1] = *reinterpret_cast<const uint32_t*>(pl + 8 * (KT + 8));
-                    al[mt][2] = *reinterpret_cast<const uint32_t*>(pl + 8), al[mt][3] = *reinterpret_cast<const uint32_t*>(pl + 8 * (KT + 8) + 8);
+                    const int poff = (mt * 16 + (lane & 15)) * (KT + 8) + 16 * ks + 8 * (lane >> 4);
+                    ldmatrix_x4(ah[mt], Ph + poff);
+                    ldmatrix_x4(al[mt], Pl + poff);
                 }
 #pragma unroll
                 for (int i = 0; i < NTW; ++i) {
@@ -831,7 +839,7 @@ int launch_latent_attention(const SeqIndex& ix, const int* cu_q, const int* seq_
     const bool tiled = ws.tiled && (d.R % 4) == 0 && (rw % 4) == 0 && d.R <= 512 &&
                        (size_t)(64 * (rw + 4)) * sizeof(float) <= 200 * 1024 &&
                        (reinterpret_cast<uintptr_t>(q_lat) & 15) == 0 && (reinterpret_cast<uintptr_t>(out_lat) & 15) == 0;
-    const bool mma = ws.tiled >= 2 && !cache.f32 && (d.R % 8) == 0 && (rw % 16) == 0 && d.R <= 512 && rw <= 832 &&
+    const bool mma = ws.tiled >= 2 && !cache.f32 && (d.R % 8) == 0 && (rw % 16) == 0 && d.R <= 512 && rw <= 768 &&
                      (reinterpret_cast<uintptr_t>(cache.pool) & 15) == 0 && (reinterpret_cast<uintptr_t>(out_lat) & 7) == 0;
     if (mma) return launch_mma(ix, cu_q, seq_slot, nseq, max_qlen, max_kv_len, q_lat, d, cache, out_lat, ws, stream);
     if (tiled)
