@@ -39,6 +39,23 @@ class MezilixConfigC(ctypes.Structure):
                 ("dtype", ctypes.c_int)]
 
 
+class RivetarLayerC(ctypes.Structure):
+    """mirror of ``asd_rivetar_layer_config``"""
+    _fields_ = [("type", ctypes.c_int), ("heads", ctypes.c_int), ("kv_heads", ctypes.c_int), ("dim", ctypes.c_int),
+                ("vdim", ctypes.c_int), ("rot_dim", ctypes.c_int), ("kv_rank", ctypes.c_int), ("q_rank", ctypes.c_int),
+                ("decay_rank", ctypes.c_int), ("rot_dims", ctypes.c_int), ("rot_interleaved", ctypes.c_int),
+                ("window", ctypes.c_int), ("keep_first", ctypes.c_int), ("rot_base", ctypes.c_float),
+                ("scale", ctypes.c_float), ("tau", ctypes.c_float), ("ff", ctypes.c_int)]
+
+
+class RivetarConfigC(ctypes.Structure):
+    """mirror of ``asd_rivetar_config``"""
+    _fields_ = [("width", ctypes.c_int), ("vocab", ctypes.c_int), ("n_layers", ctypes.c_int), ("eps", ctypes.c_float),
+                ("embed_scale", ctypes.c_float), ("logit_softcap", ctypes.c_float), ("loop_start", ctypes.c_int),
+                ("loop_stop", ctypes.c_int), ("loop_times", ctypes.c_int), ("max_tokens", ctypes.c_int),
+                ("page_size", ctypes.c_int), ("ring", ctypes.c_int), ("dtype", ctypes.c_int)]
+
+
 def library_path() -> str:
     return os.path.join(_HERE, "libasd_b200.so")
 
@@ -102,6 +119,16 @@ def lib() -> ctypes.CDLL:
         "asd_linear_tc": (i32, [vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp]),
         "asd_mezilix_device_error": (i32, [vp]),
         "asd_mezilix_profile_read": (i32, [vp, vp, vp, i32]),
+        "asd_rivetar_create": (vp, [vp, vp]),
+        "asd_rivetar_destroy": (None, [vp]),
+        "asd_rivetar_set_tensor": (i32, [vp, i32, c.c_char_p, vp]),
+        "asd_rivetar_cache_bytes": (sz, [vp, i32]),
+        "asd_rivetar_state_bytes": (sz, [vp, i32]),
+        "asd_rivetar_set_cache": (i32, [vp, vp, i32, vp, i32, i32, vp]),
+        "asd_rivetar_set_option": (i32, [vp, c.c_char_p, i32]),
+        "asd_rivetar_forward": (i32, [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, vp, i32, vp, c.c_longlong, vp, vp]),
+        "asd_rivetar_profile_read": (i32, [vp, vp, vp, i32]),
+        "asd_rivetar_device_error": (i32, [vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(L, name, None)

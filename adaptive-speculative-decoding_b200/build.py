@@ -23,11 +23,13 @@ FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-li
 COMPONENTS = {
     "core": ["core.cu"],
     "linear": ["gemm.cu", "gemm_tc.cu"],
-    "mezilix": ["mezilix_engine.cu", "linear_simt.cu", "linear_tc.cu", "stream_ops.cu", "latent_attention.cu", "moe.cu"],
+    "blocks": ["linear_simt.cu", "linear_tc.cu", "latent_attention.cu"],
+    "mezilix": ["mezilix_engine.cu", "stream_ops.cu", "moe.cu"],
+    "rivetar": ["rivetar_engine.cu", "norm_ops.cu", "gla.cu", "window_attention.cu"],
     "qwen": ["engine.cu", "layers.cu", "attention.cu", "attention_tc.cu", "forward_persist.cu"],
     "sampling": ["api.cu", "sampler.cu", "stop_rule.cu"],
 }
-REQUIRES = {"mezilix": ("linear",), "qwen": ("linear",)}
+REQUIRES = {"mezilix": ("linear", "blocks"), "rivetar": ("linear", "blocks"), "qwen": ("linear",)}
 
 
 def all_components():

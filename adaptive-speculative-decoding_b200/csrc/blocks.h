@@ -1,5 +1,6 @@
 // Host-side launchers of the sequence-model building blocks that take their sizes and constants as arguments
-// (linear_simt.cu, stream_ops.cu, latent_attention.cu, moe.cu).  An engine (mezilix_engine.cu) strings them together;
+// (linear_simt.cu, stream_ops.cu, latent_attention.cu, moe.cu, norm_ops.cu, gla.cu, window_attention.cu).  An engine
+// (mezilix_engine.cu, rivetar_engine.cu) strings them together;
 // none of them knows a model.  `f32` flags select the element type of a buffer: 0 = bf16, 1 = fp32.  Norms, scores,
 // softmax weights, router probabilities, the residual stream and the carried state are fp32 in both modes.
 #pragma once
@@ -97,6 +98,7 @@ struct LatentDims {
     int rot_dims;               // leading coordinates of the rotated part that rotate (pairs i, i + rot_dims / 2)
     int window;                 // position p sees p - window < j <= p
     float scale;
+    int interleaved = 0;        // 1: the rotating pairs are (2 i, 2 i + 1) instead of (i, i + rot_dims / 2)
 };
 struct PagedRows {
     void* pool;                // this layer's rows: [num_pages][page_size][row_elems]
@@ -109,6 +111,11 @@ struct PagedRows {
 // q_lat[m][head][R .. R + dr) (fp32, row length R + dr).  inv_freq fp32 [rot_dims / 2].
 int launch_latent_post(const SeqIndex& ix, const float* qd, const LatentDims& d, const void* c_norm, int wf32, float eps,
                        const float* inv_freq, const PagedRows& cache, float* q_lat, cudaStream_t stream);
+// The same with the queries and the (latent | rotated key) part in buffers of their own: q fp32 rows of ldq floats
+// (heads * (dn + dr) used), kv fp32 rows of ldkv floats (R + dr used).
+int launch_latent_post_split(const SeqIndex& ix, const float* q, long long ldq, const float* kv, long long ldkv,
+                             const LatentDims& d, const void* c_norm, int wf32, float eps, const float* inv_freq,
+                             const PagedRows& cache, float* q_lat, cudaStream_t stream);
 // Workspace of the register-tiled kernel when it cuts a long key range into shares (few query rows, long context):
 // o [o_elems] floats, ml [2 * rows] floats; (token, head) pairs x shares must fit `rows`.  tiled = 0 forces the
 // one-warp-per-pair kernel, which takes any latent size; 1 the register-tiled fp32 kernel where the sizes allow; 2 (default)
@@ -140,6 +147,85 @@ struct MoeRouterInput {
 };
 int launch_moe_route(const float* logits, const MoeRouterInput* in, int M, int E, int top, int* expert_of, float* gate,
                      int* counters, int* group_off, int* sorted_tok, int* slot_of, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------- norm_ops.cu
+// Row kernels of sandwich-normed layers (a norm before and after every sublayer).  "Offset" RMS norms store their
+// weight as the deviation from one: x / sqrt(mean(x^2) + eps) * (1 + w).  Norm weights are fp32 vectors.
+// x0[m] = embed[token] * scale, fp32 (x, if given, receives a copy: the stream that the layers go on to change)
+int launch_embed_scaled(const SeqIndex& ix, const void* embed, int wf32, float scale, float* x0, float* x, int D,
+                        cudaStream_t stream);
+// Closes a sublayer and prepares the next one in one pass over a row:
+//   x_out = x_in + (post_w ? y / rms(y) * (1 + post_w) : y) + bias          (each term optional)
+//   hn    = x_out / rms(x_out) * (1 + next_w)   in the engine's element type (if next_w)
+//   hn    = [x_out | cat[m]]                     rows of 2 D elements        (if cat: input of a pass-entry projection)
+struct RowClose {
+    const float* x_in = nullptr;    // [M][D]; with `rows`: row r reads x_in[rows[r]]
+    const int* rows = nullptr;
+    const float* y = nullptr;       // [M][D]
+    const float* post_w = nullptr;  // [D]
+    const float* bias = nullptr;    // [D]
+    float* x_out = nullptr;         // [M][D], may alias x_in
+    const float* next_w = nullptr;  // [D]
+    const float* cat = nullptr;     // [M][D]
+    void* hn = nullptr;
+    int hn_f32 = 0;
+    float eps = 0.f;
+    int M = 0, D = 0;
+};
+int launch_row_close(const RowClose& c, cudaStream_t stream);
+// out[m][0 .. n) = in[m][0 .. n) / rms * w (plain weight; plus_one: 1 + w), rows ld_in / ld_out apart
+int launch_rms_rows(const float* in, long long ld_in, const float* w, int plus_one, float eps, void* out, int of32,
+                    long long ld_out, int M, int n, cudaStream_t stream);
+// Normalised cubic polynomial over a feed-forward row: a N(z) + b N(z^2) + c N(z^3) + e with powers taken element by
+// element, N(u) = u / sqrt(mean(u^2) + eps) and coeff = (a, b, c, e) fp32.
+int launch_polynorm(const float* z, const float* coeff, float eps, void* out, int of32, int M, int F, cudaStream_t stream);
+// logits <- cap * tanh(logits / cap) in place, n rows of V floats ld apart
+int launch_softcap(float* logits, long long ld, int n, int V, float cap, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------- gla.cu
+// Gated linear attention: per head a state S [dk][dv] in fp32 with a decay per key channel,
+//   S_t = diag(alpha_t) S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t,   alpha = sigmoid(z)^(1 / tau).
+struct GlaDims {
+    int heads, dk, dv;
+    int low;        // inner size of the decay projection
+    float tau;
+    float q_scale;  // applied to q inside the recurrence
+};
+// alpha[m][heads * dk] = exp(log_sigmoid(w_decay . a[m] + b_decay) / tau); a = fp32 rows of `low` floats lda apart
+int launch_gla_decay(const float* a, long long lda, const float* w_decay, const float* b_decay, const GlaDims& d,
+                     float* alpha, int M, cudaStream_t stream);
+// state fp32 [slots][ring][heads][dk][dv]; entry position % ring holds the state after that position.  A sequence whose
+// first new position is 0 starts from zero, any other from entry (position - 1) % ring; the last `ring` new positions
+// of a sequence store theirs.  q, k (heads * dk used) and v (heads * dv used) are fp32 rows ld floats apart.
+// out fp32 [M][heads * dv].
+int launch_gla_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, const float* q,
+                          const float* k, const float* v, long long ld, const float* alpha, const GlaDims& d,
+                          float* state, int ring, float* out, cudaStream_t stream);
+// y[m][h][:] = o[m][h][:] / rms(o[m][h][:]) * w * silu(gate[m][h][:]) in the engine's element type
+int launch_gla_out(const float* o, const float* gate, long long ldg, const float* w, float eps, void* y, int of32, int M,
+                   int heads, int dv, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------- window_attention.cu
+// Grouped-query softmax attention over a sliding window plus kept first positions, with a sink in the denominator and
+// position-rotated values.  Cache row per position: [kv_heads * dk rotated keys | kv_heads * dv rotated values].
+struct WindowDims {
+    int heads, kv_heads, dk, dv;
+    int rot_dims;      // leading key/query coordinates that rotate; the values rotate over all dv
+    int interleaved;   // pairs (2 i, 2 i + 1) or (i, i + n / 2)
+    int window;        // position i sees j <= i with i - j < window ...
+    int keep_first;    // ... or j < keep_first
+    float scale;
+};
+// qkv fp32 rows (ld floats apart) = [heads * dk | kv_heads * dk | kv_heads * dv].  Rotates the queries in place and
+// appends the rotated keys and values to the cache.  freq_k fp32 [rot_dims / 2], freq_v fp32 [dv / 2].
+int launch_window_post(const SeqIndex& ix, float* qkv, long long ld, const WindowDims& d, const float* freq_k,
+                       const float* freq_v, const PagedRows& cache, cudaStream_t stream);
+// out[m][heads * dv] in the engine's element type: softmax (denominator + exp(sink[head])) over the visible positions,
+// turned back by the query's position.  sink fp32 [heads] (nullptr: none).  tiled = 0: one warp per (token, head).
+int launch_window_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen,
+                            int max_kv_len, const float* q, long long ldq, const WindowDims& d, const float* sink,
+                            const float* freq_v, const PagedRows& cache, void* out, int of32, int tiled,
+                            cudaStream_t stream);
 
 int preload_blocks();
 

@@ -2,7 +2,8 @@
 // sliding window.  Scores, softmax weights and the weighted sum are fp32; the cache rows are the engine's element type.
 //
 // latent_post_kernel: one CTA per token.  RMS-norms the latent (vector weight), rotates the shared key part and the
-// rotated part of every head's query (rotate-half pairing inside the first rot_dims coordinates), appends the cache row.
+// rotated part of every head's query (pairs (i, i + rot_dims / 2) or (2 i, 2 i + 1) inside the first rot_dims coordinates),
+// appends the cache row.
 // latent_attn_kernel: one CTA per (tile of TQ consecutive query tokens, group of HG heads); every warp owns one (token,
 // head) pair for the whole key loop, the CTA stages 32 keys at a time in shared memory and all its warps share them,
 // so a prefill tile reads each key once per TQ x HG pairs and a decode step (TQ = 1) once per HG heads.  Lane j scores
@@ -23,35 +24,39 @@ __device__ __forceinline__ long long cache_row(const PagedRows& c, int slot, int
     return (long long)page * c.page_size + pos % c.page_size;
 }
 
-__global__ void latent_post_kernel(SeqIndex ix, const float* qd, LatentDims d, const void* c_norm, int wf32, float eps,
-                                   const float* inv_freq, PagedRows cache, float* q_lat) {
+__global__ void latent_post_kernel(SeqIndex ix, const float* q, long long ldq, const float* kvp, long long ldkv,
+                                   LatentDims d, const void* c_norm, int wf32, float eps, const float* inv_freq,
+                                   PagedRows cache, float* q_lat) {
     __shared__ float red[33];
     const int m = blockIdx.x;
     const int pos = ix.positions[m], slot = ix.token_slot[m];
-    const int qw = d.dn + d.dr, nq = d.heads * qw, ld = nq + d.R + d.dr, rw = d.R + d.dr;
-    const float* row = qd + (long long)m * ld;
+    const int qw = d.dn + d.dr, rw = d.R + d.dr;
+    const float* qrow = q + (long long)m * ldq;
+    const float* kv = kvp + (long long)m * ldkv;
     const long long crow = cache_row(cache, slot, pos) * rw;
     float ss = 0.f;
     for (int i = threadIdx.x; i < d.R; i += blockDim.x) {
-        const float v = row[nq + i];
+        const float v = kv[i];
         ss += v * v;
     }
     ss = block_sum(ss, red);
     const float r = 1.f / sqrtf(ss / (float)d.R + eps);
     for (int i = threadIdx.x; i < d.R; i += blockDim.x)
-        stx(cache.pool, crow + i, cache.f32, row[nq + i] * r * ldx(c_norm, i, wf32));
+        stx(cache.pool, crow + i, cache.f32, kv[i] * r * ldx(c_norm, i, wf32));
     // rotated parts: vector 0 is the shared key, vectors 1 .. heads the queries
     const int half = d.rot_dims / 2;
     for (int t = threadIdx.x; t < (d.heads + 1) * d.dr; t += blockDim.x) {
         const int vec = t / d.dr, i = t % d.dr;
-        const float* src = vec == 0 ? row + nq + d.R : row + (long long)(vec - 1) * qw + d.dn;
+        const float* src = vec == 0 ? kv + d.R : qrow + (long long)(vec - 1) * qw + d.dn;
         float out;
         if (i < d.rot_dims) {
-            const int j = i < half ? i : i - half;
+            // pair j = (a, b): coordinate a becomes u cos - v sin, coordinate b becomes v cos + u sin
+            const int j = d.interleaved ? i >> 1 : (i < half ? i : i - half);
+            const int a = d.interleaved ? 2 * j : j, b = d.interleaved ? 2 * j + 1 : j + half;
             float sn, cs;
             sincosf((float)pos * inv_freq[j], &sn, &cs);
-            const float u = src[j], v = src[j + half];
-            out = i < half ? u * cs - v * sn : v * cs + u * sn;
+            const float u = src[a], v = src[b];
+            out = i == a ? u * cs - v * sn : v * cs + u * sn;
         } else {
             out = src[i];
         }
@@ -819,15 +824,22 @@ int launch_attn_t(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int 
 
 }  // namespace
 
-int launch_latent_post(const SeqIndex& ix, const float* qd, const LatentDims& d, const void* c_norm, int wf32, float eps,
-                       const float* inv_freq, const PagedRows& cache, float* q_lat, cudaStream_t stream) {
+int launch_latent_post_split(const SeqIndex& ix, const float* q, long long ldq, const float* kv, long long ldkv,
+                             const LatentDims& d, const void* c_norm, int wf32, float eps, const float* inv_freq,
+                             const PagedRows& cache, float* q_lat, cudaStream_t stream) {
     if (ix.M <= 0) return 0;
     if (d.rot_dims < 0 || d.rot_dims > d.dr || (d.rot_dims & 1))
         return set_error("latent attention: rot_dims %d must be even and <= %d", d.rot_dims, d.dr);
-    latent_post_kernel<<<ix.M, 128, 0, stream>>>(ix, qd, d, c_norm, wf32, eps, inv_freq, cache, q_lat);
+    latent_post_kernel<<<ix.M, 128, 0, stream>>>(ix, q, ldq, kv, ldkv, d, c_norm, wf32, eps, inv_freq, cache, q_lat);
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
     return 0;
+}
+
+int launch_latent_post(const SeqIndex& ix, const float* qd, const LatentDims& d, const void* c_norm, int wf32, float eps,
+                       const float* inv_freq, const PagedRows& cache, float* q_lat, cudaStream_t stream) {
+    const int nq = d.heads * (d.dn + d.dr), ld = nq + d.R + d.dr;
+    return launch_latent_post_split(ix, qd, ld, qd + nq, ld, d, c_norm, wf32, eps, inv_freq, cache, q_lat, stream);
 }
 
 int launch_latent_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen,

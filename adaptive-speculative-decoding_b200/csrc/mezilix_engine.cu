@@ -17,6 +17,7 @@
 #include "../../include/asd_b200.h"
 #include "asd_internal.h"
 #include "blocks.h"
+#include "dense.h"
 #include "gemm.h"
 #include "prof.h"
 
@@ -50,18 +51,11 @@ struct MzEngine : asd_mezilix_engine {
     void *h = nullptr, *hs = nullptr, *vout = nullptr, *act = nullptr, *xsel = nullptr;
     int *expert_of = nullptr, *counters = nullptr, *group_off = nullptr, *sorted_tok = nullptr, *slot_of = nullptr;
     std::vector<void*> owned;
-    int tc_linear = 1;
-    int tc_min_rows = 257;       // token count from which dense projections use the tensor-bound CTA-pair GEMM
+    DenseRunner dn;              // dense projections: tcgen05 GEMMs or the CUDA-core kernel, by shape and type
     EventProfiler prof;
     AttnSplit attn_ws;           // partial sums of the attention kernel's key-range shares
     int* dev_error = nullptr;    // raised by a kernel whose bounded wait ran out
     int device = 0;
-    struct TcEntry {
-        GemmPlan pl;
-        TcPlan big;
-        CUtensorMap tw, tx;
-    };
-    std::unordered_map<unsigned long long, TcEntry> tc_cache;
 };
 
 template <typename T>
@@ -76,33 +70,7 @@ static int dev_alloc(MzEngine* e, T** p, size_t n) {
 // y fp32 [M][ldc] = x [M][K] (engine type, contiguous rows) * w[N][K]^T
 static int dense(MzEngine* e, const void* x, const void* w, float* y, int M, int N, int K, int ldc, int key,
                  cudaStream_t s) {
-    if (!e->f32 && e->tc_linear && (K % 8) == 0 && (ldc % 4) == 0 && K >= 64 && N >= 8 &&
-        (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
-        (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
-        const unsigned long long k = ((unsigned long long)key << 32) | (unsigned)M;
-        auto it = e->tc_cache.find(k);
-        if (it == e->tc_cache.end()) {
-            MzEngine::TcEntry t;
-            if (make_tmap_bf16(&t.tw, w, N, K, K, 128)) return -1;
-            if (M >= e->tc_min_rows) {   // above the HBM / tensor ridge: 256 weight rows x MT tokens on a CTA pair
-                if (gemm_tc_plan(&t.big, M, N, K, GEMM_OUT_F32, 1, 0)) return -1;
-                if (make_tmap_bf16(&t.tx, x, M, K, K, t.big.MT / 2)) return -1;
-            } else {
-                if (gemm_plan(&t.pl, M, N, K, GEMM_OUT_F32, 0, 0, 1)) return -1;
-                if (make_tmap_bf16(&t.tx, x, M, K, K, t.pl.MT)) return -1;
-            }
-            it = e->tc_cache.emplace(k, t).first;
-        }
-        if (M >= e->tc_min_rows)
-            return gemm_tc_launch(it->second.big, it->second.tw, it->second.tx, y, ldc, N, 0, false, s, false, nullptr);
-        return gemm_launch(it->second.pl, it->second.tw, it->second.tx, y, ldc, N, false, s, false);
-    }
-    SimtLinear L;
-    L.a = x, L.a_f32 = e->f32, L.lda = K;
-    L.w = w, L.w_f32 = e->f32, L.ldw = K;
-    L.c = y, L.c_f32 = 1, L.ldc = ldc;
-    L.M = M, L.N = N, L.K = K;
-    return launch_simt_linear(L, s);
+    return e->dn.run(x, w, y, M, N, K, ldc, key, s);
 }
 
 enum MzProf { MZ_DENSE = 0, MZ_HEADS = 1, MZ_ATTN = 2, MZ_EXPERTS = 3, MZ_ROUTER = 4, MZ_GLUE = 5, MZ_HEAD = 6, MZ_NCLASS = 7 };
@@ -110,7 +78,7 @@ enum MzProf { MZ_DENSE = 0, MZ_HEADS = 1, MZ_ATTN = 2, MZ_EXPERTS = 3, MZ_ROUTER
 
 // batched / grouped linear: tcgen05 in the bf16 engine when the shape allows, CUDA cores otherwise
 static int linear(MzEngine* e, const SimtLinear& L, cudaStream_t s) {
-    if (!e->f32 && e->tc_linear && tc_linear_supports(L)) return launch_tc_linear(L, e->dev_error, s);
+    if (!e->f32 && e->dn.tc_linear && tc_linear_supports(L)) return launch_tc_linear(L, e->dev_error, s);
     return launch_simt_linear(L, s);
 }
 
@@ -243,6 +211,7 @@ asd_mezilix_engine_t* asd_mezilix_create(const asd_mezilix_config* cfg, const as
     MzEngine* e = new MzEngine();
     e->c = *cfg;
     e->f32 = cfg->dtype;
+    e->dn.f32 = cfg->dtype;
     e->esz = cfg->dtype ? 4 : 2;
     cudaGetDevice(&e->device);
     const size_t MT = cfg->max_tokens, D = cfg->width;
@@ -325,7 +294,7 @@ int asd_mezilix_set_globals(asd_mezilix_engine_t* h, const void* embed, const vo
     MzEngine* e = static_cast<MzEngine*>(h);
     if (!e || !embed || !pair_table || !final_gain || !head) return set_error("asd_mezilix_set_globals: NULL argument");
     e->embed = embed, e->pair_table = pair_table, e->final_gain = final_gain, e->head = head;
-    e->tc_cache.clear();
+    e->dn.clear();
     return 0;
 }
 
@@ -340,7 +309,7 @@ int asd_mezilix_set_layer(asd_mezilix_engine_t* h, int layer, const void* gain, 
     if (ly.c.experts > 0 && (!router || !w_up || !w_down)) return set_error("asd_mezilix_set_layer: NULL expert weight");
     ly.gain = gain, ly.shift = shift, ly.coeff = depth_coeff, ly.wqd = wqd, ly.latent_gain = latent_gain, ly.wuk = wuk;
     ly.wuv = wuv, ly.wo = wo, ly.router = router, ly.w_up = w_up, ly.w_down = w_down;
-    e->tc_cache.clear();
+    e->dn.clear();
     return 0;
 }
 
@@ -373,12 +342,12 @@ int asd_mezilix_set_option(asd_mezilix_engine_t* h, const char* name, int value)
     MzEngine* e = static_cast<MzEngine*>(h);
     if (!e || !name) return set_error("asd_mezilix_set_option: NULL argument");
     if (!strcmp(name, "tc_linear")) {
-        e->tc_linear = value;
+        e->dn.tc_linear = value;
         return 0;
     }
     if (!strcmp(name, "tc_min_rows")) {
-        e->tc_min_rows = value > 0 ? value : 1 << 30;
-        e->tc_cache.clear();
+        e->dn.tc_min_rows = value > 0 ? value : 1 << 30;
+        e->dn.clear();
         return 0;
     }
     if (!strcmp(name, "attn_tiled")) {

@@ -1,0 +1,153 @@
+// Row kernels of sandwich-normed layers: scaled embedding, the close of a sublayer fused with the norm that follows
+// (residual sum, norm after the sublayer, norm before the next one, optionally the concatenation a pass entry reads),
+// plain / offset RMS norm of a slice of a row, the normalised cubic polynomial of a feed-forward row, the tanh cap of
+// the logits.  One CTA per row; sums of squares, the residual stream and every norm are fp32 whatever the engine's type.
+#include <cuda_bf16.h>
+
+#include "asd_internal.h"
+#include "blocks.h"
+#include "elem.cuh"
+
+namespace asd {
+
+namespace {
+
+inline int row_threads(int D) { return D >= 2048 ? 512 : (D >= 1024 ? 256 : (D >= 256 ? 128 : 64)); }
+
+__global__ void embed_scaled_kernel(SeqIndex ix, const void* embed, int wf32, float scale, float* x0, float* x, int D) {
+    const int m = blockIdx.x;
+    const long long src = (long long)ix.tokens[m] * D, dst = (long long)m * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float v = ldx(embed, src + d, wf32) * scale;
+        x0[dst + d] = v;
+        if (x) x[dst + d] = v;
+    }
+}
+
+// dynamic shared memory: D floats (the row being built) + 33 for the block sums
+__global__ void row_close_kernel(RowClose c) {
+    extern __shared__ float sm[];
+    float* row = sm;
+    float* red = sm + c.D;
+    const int m = blockIdx.x, D = c.D;
+    const long long base = (long long)m * D;
+    const long long in_base = c.rows ? (long long)c.rows[m] * D : base;
+    float post = 1.f;
+    if (c.y && c.post_w) {
+        float ss = 0.f;
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            const float v = c.y[base + d];
+            ss += v * v;
+        }
+        post = 1.f / sqrtf(block_sum(ss, red) / (float)D + c.eps);
+    }
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float v = c.x_in ? c.x_in[in_base + d] : 0.f;
+        if (c.y) v += c.post_w ? c.y[base + d] * post * (1.f + c.post_w[d]) : c.y[base + d];
+        if (c.bias) v += c.bias[d];
+        row[d] = v;
+        if (c.x_out) c.x_out[base + d] = v;
+        ss += v * v;
+    }
+    if (c.next_w) {
+        const float r = 1.f / sqrtf(block_sum(ss, red) / (float)D + c.eps);
+        for (int d = threadIdx.x; d < D; d += blockDim.x) stx(c.hn, base + d, c.hn_f32, row[d] * r * (1.f + c.next_w[d]));
+    } else if (c.cat) {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            stx(c.hn, 2 * base + d, c.hn_f32, row[d]);
+            stx(c.hn, 2 * base + D + d, c.hn_f32, c.cat[base + d]);
+        }
+    }
+}
+
+__global__ void rms_rows_kernel(const float* in, long long ld_in, const float* w, int plus_one, float eps, void* out,
+                                int of32, long long ld_out, int n) {
+    __shared__ float red[33];
+    const float* src = in + (long long)blockIdx.x * ld_in;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += src[i] * src[i];
+    const float r = 1.f / sqrtf(block_sum(ss, red) / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        stx(out, (long long)blockIdx.x * ld_out + i, of32, src[i] * r * (plus_one ? 1.f + w[i] : w[i]));
+}
+
+__global__ void polynorm_kernel(const float* z, const float* coeff, float eps, void* out, int of32, int F) {
+    __shared__ float red[33];
+    const float* src = z + (long long)blockIdx.x * F;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int i = threadIdx.x; i < F; i += blockDim.x) {
+        const float v = src[i], v2 = v * v, v3 = v2 * v;
+        s2 += v2;
+        s4 += v2 * v2;
+        s6 += v3 * v3;
+    }
+    s2 = block_sum(s2, red);
+    s4 = block_sum(s4, red);
+    s6 = block_sum(s6, red);
+    const float inv = 1.f / (float)F;
+    const float a = coeff[0] / sqrtf(s2 * inv + eps), b = coeff[1] / sqrtf(s4 * inv + eps),
+                c = coeff[2] / sqrtf(s6 * inv + eps), e = coeff[3];
+    for (int i = threadIdx.x; i < F; i += blockDim.x) {
+        const float v = src[i], v2 = v * v;
+        stx(out, (long long)blockIdx.x * F + i, of32, a * v + b * v2 + c * (v2 * v) + e);
+    }
+}
+
+__global__ void softcap_kernel(float* logits, long long ld, int V, float cap) {
+    float* row = logits + (long long)blockIdx.x * ld;
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
+    if (i < V) row[i] = cap * tanhf(row[i] / cap);
+}
+
+}  // namespace
+
+int launch_embed_scaled(const SeqIndex& ix, const void* embed, int wf32, float scale, float* x0, float* x, int D,
+                        cudaStream_t stream) {
+    if (ix.M <= 0) return 0;
+    embed_scaled_kernel<<<ix.M, row_threads(D), 0, stream>>>(ix, embed, wf32, scale, x0, x, D);
+    count_launch(1);
+    ASD_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_row_close(const RowClose& c, cudaStream_t stream) {
+    if (c.M <= 0) return 0;
+    if (c.D <= 0 || ((c.next_w || c.cat) && !c.hn)) return set_error("row_close: bad arguments");
+    const size_t smem = (size_t)(c.D + 33) * sizeof(float);
+    if (smem > 200 * 1024) return set_error("row_close: width %d does not fit shared memory", c.D);
+    if (smem > 48 * 1024)
+        ASD_CUDA(cudaFuncSetAttribute(row_close_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    row_close_kernel<<<c.M, row_threads(c.D), smem, stream>>>(c);
+    count_launch(1);
+    ASD_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_rms_rows(const float* in, long long ld_in, const float* w, int plus_one, float eps, void* out, int of32,
+                    long long ld_out, int M, int n, cudaStream_t stream) {
+    if (M <= 0 || n <= 0) return 0;
+    rms_rows_kernel<<<M, row_threads(n), 0, stream>>>(in, ld_in, w, plus_one, eps, out, of32, ld_out, n);
+    count_launch(1);
+    ASD_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_polynorm(const float* z, const float* coeff, float eps, void* out, int of32, int M, int F, cudaStream_t stream) {
+    if (M <= 0 || F <= 0) return 0;
+    polynorm_kernel<<<M, row_threads(F), 0, stream>>>(z, coeff, eps, out, of32, F);
+    count_launch(1);
+    ASD_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_softcap(float* logits, long long ld, int n, int V, float cap, cudaStream_t stream) {
+    if (n <= 0 || V <= 0 || !(cap > 0.f)) return 0;
+    dim3 grid(n, (V + 255) / 256);
+    softcap_kernel<<<grid, 256, 0, stream>>>(logits, ld, V, cap);
+    count_launch(1);
+    ASD_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace asd

@@ -10,7 +10,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ._lib import AsdError, MezilixConfigC, MezilixLayerC, ModelConfigC, check, lib
+from ._lib import AsdError, MezilixConfigC, MezilixLayerC, ModelConfigC, RivetarConfigC, RivetarLayerC, check, lib
 from .models.qwen2 import Qwen2Config, pack_layer, random_packed_layer
 from .ops import NUM_FEATURES
 
@@ -418,7 +418,32 @@ def _remote_forward(eng, dev, tokens, positions, token_slot, cu_q, seq_slot, max
     return logits_out if n_rows else None
 
 
-class MezilixEngine(_BatchOps):
+class _SlotOps:
+    """Sequences of an engine whose cache is a ``PageTable`` (``self.pages``) and whose carried state is indexed by slot."""
+
+    def open_sequence(self) -> int:
+        """a free slot (dynamic page table); its first forward starts at position 0, which resets the carried state"""
+        return self.pages.alloc_slot()
+
+    def close_sequence(self, slot: int) -> None:
+        self.pages.free_slot(slot)
+
+    def reserve(self, slot: int, n_tokens: int) -> None:
+        if n_tokens > self.max_seq_len:
+            raise AsdError(f"sequence of {n_tokens} tokens exceeds max_seq_len {self.max_seq_len}")
+        self.pages.reserve(slot, n_tokens)
+
+    def _check_forward_args(self, tensors, max_kv_len: int) -> None:
+        for t in tensors:
+            assert t.dtype == torch.int32 and t.is_contiguous() and t.is_cuda, "int32 contiguous CUDA tensors"
+            if t.device != self.device:
+                raise AsdError(f"{type(self).__name__}.forward: inputs must live on the engine's device")
+        if max_kv_len > self.max_pages * self.page_size:
+            raise AsdError(f"sequence length bound {max_kv_len} exceeds this engine's max_seq_len "
+                           f"{self.max_pages * self.page_size} (page-table overrun refused)")
+
+
+class MezilixEngine(_SlotOps, _BatchOps):
     """One Mezilix-family model on one GPU: wraps an ``asd_mezilix_engine_t`` handle and owns what a sequence carries
     between forwards: the paged latent cache (``PageTable``; dynamic by default, static for uniform benchmark
     batches), the ring of recent tokens (the embedding hashes the previous token) and, per layer, the ring of recent
@@ -526,19 +551,6 @@ class MezilixEngine(_BatchOps):
         """raises if a kernel of this engine gave up a bounded wait (synchronises)"""
         check(lib().asd_mezilix_device_error(self.h), "asd_mezilix_device_error")
 
-    # ------------------------------------------------------------------ sequences
-    def open_sequence(self) -> int:
-        """a free slot (dynamic page table); its first forward starts at position 0, which resets the carried state"""
-        return self.pages.alloc_slot()
-
-    def close_sequence(self, slot: int) -> None:
-        self.pages.free_slot(slot)
-
-    def reserve(self, slot: int, n_tokens: int) -> None:
-        if n_tokens > self.max_seq_len:
-            raise AsdError(f"sequence of {n_tokens} tokens exceeds max_seq_len {self.max_seq_len}")
-        self.pages.reserve(slot, n_tokens)
-
     # ------------------------------------------------------------------ forward
     def forward(self, tokens, positions, token_slot, cu_q, seq_slot, max_qlen: int, max_kv_len: int,
                 logit_rows: Optional[torch.Tensor] = None, logits_out: Optional[torch.Tensor] = None,
@@ -546,13 +558,7 @@ class MezilixEngine(_BatchOps):
         """int32 CUDA tensors on this engine's device; returns fp32 logits [rows, vocab] (or None).  With
         ``layer_out`` also the stream that leaves every layer, fp32 [layers, M, width]."""
         M, nseq = tokens.numel(), seq_slot.numel()
-        for t in (tokens, positions, token_slot, cu_q, seq_slot):
-            assert t.dtype == torch.int32 and t.is_contiguous() and t.is_cuda, "int32 contiguous CUDA tensors"
-            if t.device != self.device:
-                raise AsdError("MezilixEngine.forward: inputs must live on the engine's device")
-        if max_kv_len > self.max_pages * self.page_size:
-            raise AsdError(f"sequence length bound {max_kv_len} exceeds this engine's max_seq_len "
-                           f"{self.max_pages * self.page_size} (page-table overrun refused)")
+        self._check_forward_args((tokens, positions, token_slot, cu_q, seq_slot), max_kv_len)
         n_rows = 0 if not want_logits else (M if logit_rows is None else logit_rows.numel())
         if n_rows and logits_out is None:
             logits_out = torch.empty(n_rows, self.cfg.vocab_size, dtype=torch.float32, device=self.device)
@@ -568,6 +574,141 @@ class MezilixEngine(_BatchOps):
                 None if not n_rows else logits_out.data_ptr(), logits_ld,
                 None if streams is None else streams.data_ptr(), _stream())
         check(rc, "asd_mezilix_forward")
+        res = logits_out if n_rows else None
+        return (res, streams) if layer_out else res
+
+
+class RivetarEngine(_SlotOps, _BatchOps):
+    """One Rivetar-family model on one GPU: wraps an ``asd_rivetar_engine_t`` handle and owns what a sequence carries
+    between forwards, per layer EXECUTION (a layer of a repeated span executes several times, each with its own):
+    the paged caches of the attention mixers (``PageTable``; latent rows, or rotated keys and values) and the
+    recurrent state of the gated-linear-attention mixers, fp32 [slot][ring][heads][dim][vdim].  Entry position % ring
+    is the state after that position, so re-feeding any of the last ``ring`` positions - what speculative
+    verification does after a rejected tail - continues from the right state; a forward that starts a slot at
+    position 0 starts from zero, so reused slots carry nothing over.
+    ``dtype``: torch.bfloat16 (bf16 matrices / caches / matrix inputs, fp32 accumulation) or torch.float32 (true fp32
+    everywhere).  Same ``forward`` contract as ``QwenEngine``, so ``SpecDecoder`` and ``Stage`` drive it unchanged."""
+
+    TYPE_CODE = {"latent_attention": 0, "gla": 1, "attention": 2}
+
+    def __init__(self, cfg, max_seqs: int, max_seq_len: int, max_tokens: int = 1024, page_size: int = 16,
+                 device="cuda", dtype=torch.bfloat16, ring: int = 1, num_pages: Optional[int] = None,
+                 dynamic_pages: bool = False, shuffle_pages: bool = True):
+        if not torch.cuda.is_available():
+            raise AsdError("RivetarEngine needs a CUDA device (there is no CPU fallback)")
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise AsdError(f"RivetarEngine runs in bfloat16 or float32, not {dtype}")
+        dev = torch.device(device)
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        self.cfg, self.device, self.dtype = cfg, dev, dtype
+        self.tp_rank, self.tp_size = 0, 1
+        self.max_seqs, self.max_seq_len, self.max_tokens, self.page_size = max_seqs, max_seq_len, max_tokens, page_size
+        self.ring = int(ring)
+        loop = cfg.loop or (0, 0, 0)
+        self.c = RivetarConfigC(cfg.width, cfg.vocab_size, cfg.num_hidden_layers, cfg.eps, cfg.embed_scale,
+                                cfg.logit_softcap, loop[0], loop[1], loop[2], max_tokens, page_size, self.ring,
+                                1 if dtype == torch.float32 else 0)
+        arr = (RivetarLayerC * max(1, cfg.num_hidden_layers))()
+        for i, l in enumerate(cfg.layers):
+            if l.type == "gla" and l.decay_rank <= 0:
+                raise AsdError(f"layer {i}: the inner size of the decay projection is unknown (a checkpoint's tensor shapes "
+                               "give it: RivetarConfig.with_shapes)")
+            arr[i] = RivetarLayerC(self.TYPE_CODE[l.type], l.heads, l.kv_heads, l.dim, l.vdim, l.rot_dim, l.kv_rank,
+                                   l.q_rank, l.decay_rank, l.rot_dims, 1 if l.rot_layout == "interleaved" else 0,
+                                   min(l.window, 1 << 30), l.keep_first, l.rot_base, l.scale, l.tau, l.ff)
+        self._lock = threading.Lock()
+        with torch.cuda.device(self.device):
+            self.h = lib().asd_rivetar_create(ctypes.byref(self.c), arr)
+        if not self.h:
+            check(-1, "asd_rivetar_create")
+        self.n_runs = len(cfg.runs())
+        self.max_pages = (max_seq_len + page_size - 1) // page_size
+        self.pages = PageTable(max_seqs, self.max_pages, page_size, self.device, num_pages=num_pages,
+                               dynamic=dynamic_pages, shuffle=shuffle_pages)
+        self.num_pages = self.pages.num_pages
+        self.cache_pool = torch.zeros(max(lib().asd_rivetar_cache_bytes(self.h, self.num_pages), 16), dtype=torch.uint8,
+                                      device=self.device)
+        self.state = torch.zeros(max(lib().asd_rivetar_state_bytes(self.h, max_seqs) // 4, 4), dtype=torch.float32,
+                                 device=self.device)
+        check(lib().asd_rivetar_set_cache(self.h, self.cache_pool.data_ptr(), self.num_pages, self.pages.table.data_ptr(),
+                                          max_seqs, self.max_pages, self.state.data_ptr()), "asd_rivetar_set_cache")
+        self._weights = {}
+        self._index_cache = {}
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().asd_rivetar_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def max_qlen(self) -> int:
+        return self.max_tokens          # every mixer's kernels tile any number of new positions
+
+    # ------------------------------------------------------------------ weights
+    def load_weights(self, w: Dict[str, torch.Tensor]):
+        """state dict with the checkpoint's tensor names (any device, any float type) -> engine buffers"""
+        from .models.rivetar import pack
+        try:
+            packed = pack(w, self.cfg, self.device, self.dtype)
+        except (KeyError, ValueError) as e:
+            raise AsdError(str(e)) from e
+        for (layer, name), t in packed.items():
+            check(lib().asd_rivetar_set_tensor(self.h, layer, name.encode(), t.data_ptr()), "asd_rivetar_set_tensor")
+        self._weights = packed
+        return self
+
+    load_hf_weights = load_weights
+
+    def load_random(self, seed: int, std: float = 0.02):
+        from .models.rivetar import random_weights
+        return self.load_weights(random_weights(self.cfg, seed, device=self.device))
+
+    def set_option(self, name: str, value: int):
+        check(lib().asd_rivetar_set_option(self.h, name.encode(), int(value)), "asd_rivetar_set_option")
+
+    PROFILE_CLASSES = ("dense", "head_products", "latent_attention", "window_attention", "recurrence", "activation",
+                       "glue", "lm_head")
+
+    def profile_read(self):
+        """(ms, launches) per kernel class since the last read; needs set_option('profile', 1)."""
+        n = len(self.PROFILE_CLASSES)
+        ms, cnt = (ctypes.c_float * n)(), (ctypes.c_int * n)()
+        check(lib().asd_rivetar_profile_read(self.h, ms, cnt, n), "asd_rivetar_profile_read")
+        return {c: (ms[i], cnt[i]) for i, c in enumerate(self.PROFILE_CLASSES)}
+
+    def check_device(self) -> None:
+        """raises if a kernel of this engine gave up a bounded wait (synchronises)"""
+        check(lib().asd_rivetar_device_error(self.h), "asd_rivetar_device_error")
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, tokens, positions, token_slot, cu_q, seq_slot, max_qlen: int, max_kv_len: int,
+                logit_rows: Optional[torch.Tensor] = None, logits_out: Optional[torch.Tensor] = None,
+                want_logits: bool = True, logits_ld: int = 0, layer_out: bool = False):
+        """int32 CUDA tensors on this engine's device; returns fp32 logits [rows, vocab] (or None).  With
+        ``layer_out`` also the stream that leaves every layer execution, fp32 [executions, M, width]."""
+        M, nseq = tokens.numel(), seq_slot.numel()
+        self._check_forward_args((tokens, positions, token_slot, cu_q, seq_slot), max_kv_len)
+        n_rows = 0 if not want_logits else (M if logit_rows is None else logit_rows.numel())
+        if n_rows and logits_out is None:
+            logits_out = torch.empty(n_rows, self.cfg.vocab_size, dtype=torch.float32, device=self.device)
+        if n_rows and logits_out.device != self.device:
+            raise AsdError("logits_out must live on the engine's device")
+        streams = (torch.empty(self.n_runs, M, self.cfg.width, dtype=torch.float32, device=self.device)
+                   if layer_out else None)
+        with self._lock, torch.cuda.device(self.device):
+            rc = lib().asd_rivetar_forward(
+                self.h, tokens.data_ptr(), positions.data_ptr(), token_slot.data_ptr(), M, cu_q.data_ptr(),
+                seq_slot.data_ptr(), nseq, max_qlen, max_kv_len,
+                None if logit_rows is None else logit_rows.data_ptr(), n_rows,
+                None if not n_rows else logits_out.data_ptr(), logits_ld,
+                None if streams is None else streams.data_ptr(), _stream())
+        check(rc, "asd_rivetar_forward")
         res = logits_out if n_rows else None
         return (res, streams) if layer_out else res
 

@@ -1,6 +1,6 @@
 """Model registry: which configuration class, engine class and library components serve a checkpoint.
 
-A checkpoint directory is recognised by its ``config.json``: ``"architecture": "Mezilix"`` or the Hugging Face keys
+A checkpoint directory is recognised by its ``config.json``: ``"architecture": "Mezilix"`` / ``"Rivetar"`` or the Hugging Face keys
 ``architectures`` / ``model_type`` of the Qwen2 family (what the reference hands to vLLM,
 src/serving/real_model_pipeline.py:98-108).  ``Stage``, the trace runner and ``bench.py`` all go through here."""
 from __future__ import annotations
@@ -35,6 +35,11 @@ def _mezilix_cfg(d: dict, name: str = "mezilix"):
     return MezilixConfig.from_dict(d, name=name)
 
 
+def _rivetar_cfg(d: dict, name: str = "rivetar"):
+    from .rivetar import RivetarConfig
+    return RivetarConfig.from_dict(d, name=name)
+
+
 def _qwen_engine():
     from ..engine import QwenEngine
     return QwenEngine
@@ -45,9 +50,15 @@ def _mezilix_engine():
     return MezilixEngine
 
 
+def _rivetar_engine():
+    from ..engine import RivetarEngine
+    return RivetarEngine
+
+
 FAMILIES: Dict[str, Family] = {
     "qwen2": Family("qwen2", ("linear", "qwen", "sampling"), ("bfloat16",), _qwen_cfg, _qwen_engine),
     "mezilix": Family("mezilix", ("mezilix",), ("bfloat16", "float32"), _mezilix_cfg, _mezilix_engine),
+    "rivetar": Family("rivetar", ("rivetar",), ("bfloat16", "float32"), _rivetar_cfg, _rivetar_engine),
 }
 
 
@@ -63,7 +74,21 @@ def family_of_dict(d: dict) -> Family:
 
 
 def family_of_config(cfg) -> Family:
-    return FAMILIES["mezilix" if getattr(cfg, "architecture", None) == "Mezilix" else "qwen2"]
+    arch = getattr(cfg, "architecture", None)
+    return FAMILIES[arch.lower() if isinstance(arch, str) and arch.lower() in FAMILIES else "qwen2"]
+
+
+def safetensors_shapes(path: str) -> Dict[str, tuple]:
+    """tensor name -> shape from the headers of a checkpoint directory's ``*.safetensors`` files (no data is read)"""
+    import glob
+    import struct
+    out: Dict[str, tuple] = {}
+    for fn in sorted(glob.glob(os.path.join(path, "*.safetensors"))):
+        with open(fn, "rb") as f:
+            (n,) = struct.unpack("<Q", f.read(8))
+            header = json.loads(f.read(n))
+        out.update({k: tuple(v["shape"]) for k, v in header.items() if k != "__metadata__"})
+    return out
 
 
 def read_config(path: str):
@@ -71,7 +96,10 @@ def read_config(path: str):
     with open(os.path.join(path, "config.json")) as f:
         d = json.load(f)
     fam = family_of_dict(d)
-    return fam, fam.config_from_dict(d, name=os.path.basename(os.path.normpath(path)) or fam.name)
+    cfg = fam.config_from_dict(d, name=os.path.basename(os.path.normpath(path)) or fam.name)
+    if hasattr(cfg, "with_shapes"):          # sizes that only a tensor's shape gives
+        cfg = cfg.with_shapes(safetensors_shapes(path))
+    return fam, cfg
 
 
 def has_config(path: str) -> bool:

@@ -3,7 +3,7 @@
 reference does not ship; the signatures below are reconstructed from those call sites and from the
 listing in docs/guides/RESEARCH_PROTOCOL.md:233-304.  Where the reference's
 Stage wraps ``vllm.LLM`` this one wraps a B200 engine chosen by the model registry (``QwenEngine`` for the Qwen2
-family, ``MezilixEngine`` for the Mezilix family), optionally accelerated by a smaller draft engine through chain
+family, ``MezilixEngine`` / ``RivetarEngine`` for the Mezilix / Rivetar families), optionally accelerated by a smaller draft engine through chain
 draft-then-verify (``SpecDecoder``)."""
 from __future__ import annotations
 
@@ -204,6 +204,10 @@ class Stage:
                 # the carried-state rings must cover the k + 1 positions a verify step may re-feed
                 self.engine = self.family.engine()(self.cfg, max_seqs=max_batch, max_seq_len=max_model_len,
                                                    max_tokens=mt, device=f"cuda:{self.gpu_ids[0]}", ring=max(8, k + 2))
+            elif self.family.name == "rivetar":
+                # the recurrent-state ring must cover the positions a draft / verify step may re-feed
+                self.engine = self.family.engine()(self.cfg, max_seqs=max_batch, max_seq_len=max_model_len,
+                                                   max_tokens=mt, device=f"cuda:{self.gpu_ids[0]}", ring=max(2, k + 2))
             elif self.tensor_parallel_size == 1:
                 self.engine = QwenEngine(self.cfg, max_seqs=max_batch, max_seq_len=max_model_len, max_tokens=mt,
                                          device=f"cuda:{self.gpu_ids[0]}")

@@ -317,6 +317,78 @@ ASD_API int asd_linear_tc(const void* x, int x_f32, const void* w, void* y, int 
 ASD_API int asd_linear_simt(const void* x, int x_f32, const void* w, int w_f32, void* y, int y_f32, int M, int N, int K,
                             void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Rivetar family engine: sandwich-normed layers, x += norm_b(f(norm(x))) for the mixer and then for the feed-forward,
+ * every such norm an RMS norm with weight (1 + w).  A layer has ONE of three mixers (type):
+ *   0 latent attention    queries through a normed latent, keys / values rebuilt from a cached normed latent plus one
+ *                         rotated key part shared by the heads (evaluated in latent space, as in the Mezilix engine);
+ *   1 gated linear attention   per head a state S [dim][vdim]: S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T q_t, with
+ *                         alpha = sigmoid(z)^(1 / tau), z a two-matrix projection plus bias; o is RMS-normed per head,
+ *                         multiplied by silu(gate) and projected;
+ *   2 windowed attention  grouped-query softmax attention; position i sees j <= i with i - j < window or
+ *                         j < keep_first; the denominator also holds exp(sink[head]); values are cached rotated by their
+ *                         own position over all vdim coordinates and a head's result is turned back by the query's.
+ * The feed-forward is W_down act(W_up h) with act = a N(z) + b N(z^2) + c N(z^3) + e, N = division by the root mean
+ * square over ff (ff == 0: none).  Layers loop_start .. loop_stop - 1 run loop_times times with the same weights
+ * (loop_times == 0: no repeated span); every execution ("run") has its own cache or state, and a pass starts with
+ * x <- W_loop [x; x0] + step[pass], x0 the embedding output.  logits <- cap * tanh(logits / cap) when cap > 0.
+ *
+ * dtype 0: bf16 matrices, caches and matrix inputs with fp32 accumulation; dtype 1: everything fp32 (CUDA-core FMA).
+ * In both, norms, angles, scores, softmax, decays, the recurrent state and the residual stream are fp32.
+ * Paged pool: per run with a positional cache [num_pages][page_size][row], row = kv_rank + rot_dim (type 0) or
+ * kv_heads * (dim + vdim) (type 2, keys then values), runs back to back.  Recurrent state (type 1, caller allocated,
+ * fp32): per run [max_seqs][ring][heads][dim][vdim], entry position % ring holds the state AFTER that position, so a
+ * caller may re-feed any of the last `ring` positions; a run that starts at position 0 starts from zero.
+ */
+typedef struct asd_rivetar_layer_config {
+    int type;                               /* 0 latent attention, 1 gated linear attention, 2 windowed attention */
+    int heads, kv_heads, dim, vdim;         /* dim: query/key size per head (type 0: the unrotated part) */
+    int rot_dim, kv_rank, q_rank;           /* type 0 */
+    int decay_rank;                         /* type 1: inner size of the decay projection */
+    int rot_dims, rot_interleaved;          /* rotating leading coordinates; pairs (2i, 2i+1) or (i, i + rot_dims/2) */
+    int window, keep_first;
+    float rot_base, scale, tau;
+    int ff;
+} asd_rivetar_layer_config;
+typedef struct asd_rivetar_config {
+    int width, vocab, n_layers;
+    float eps, embed_scale, logit_softcap;
+    int loop_start, loop_stop, loop_times;
+    int max_tokens, page_size, ring, dtype;
+} asd_rivetar_config;
+typedef struct asd_rivetar_engine asd_rivetar_engine_t;
+
+ASD_API asd_rivetar_engine_t* asd_rivetar_create(const asd_rivetar_config* cfg, const asd_rivetar_layer_config* layers);
+ASD_API void asd_rivetar_destroy(asd_rivetar_engine_t* e);
+/* Weights by name; matrices row-major [out, in] in the engine's dtype, vectors always fp32.  layer -1: "embed"
+ * [vocab, width], "final_norm" [width], "head" [vocab, width], "loop_in" [width, 2 width], "loop_step" [times, width].
+ * Every layer: "norm1", "norm1b" (and "norm2", "norm2b", "w_up" [ff, width], "w_down" [width, ff], "act" [4] when
+ * ff > 0), "w_o" [width, heads * vdim], "w_in" = the matrices that read the mixer input stacked by rows:
+ *   type 0: [q_rank | kv_rank + rot_dim]; also "q_norm" [q_rank], "kv_norm" [kv_rank], "w_uq" [heads * (dim + rot_dim),
+ *           q_rank], "w_uk" [heads][kv_rank][dim] (transposed per head), "w_uv" [heads * vdim, kv_rank];
+ *   type 1: [q | k | v | gate | decay-in]; also "w_decay" fp32 [heads * dim, decay_rank], "b_decay" [heads * dim],
+ *           "out_norm" [vdim];
+ *   type 2: [q | k | v]; also "sink" [heads]. */
+ASD_API int asd_rivetar_set_tensor(asd_rivetar_engine_t* e, int layer, const char* name, const void* data);
+ASD_API size_t asd_rivetar_cache_bytes(const asd_rivetar_engine_t* e, int num_pages);
+ASD_API size_t asd_rivetar_state_bytes(const asd_rivetar_engine_t* e, int max_seqs);
+ASD_API int asd_rivetar_set_cache(asd_rivetar_engine_t* e, void* pool, int num_pages, const int32_t* page_table,
+                                  int max_seqs, int max_pages_per_seq, float* state);
+/* options: "tc_linear", "tc_min_rows", "attn_tiled" as for the Mezilix engine; "fused_attn" (1, default: tiled windowed
+ * attention kernel; 0: one warp per (token, head)); "profile" */
+ASD_API int asd_rivetar_set_option(asd_rivetar_engine_t* e, const char* name, int value);
+/* Same contract as asd_engine_forward (M <= max_tokens).  layer_out (optional, fp32 [runs][M][width]) receives the
+ * stream that leaves every layer execution. */
+ASD_API int asd_rivetar_forward(asd_rivetar_engine_t* e, const int32_t* tokens, const int32_t* positions,
+                                const int32_t* token_slot, int M, const int32_t* cu_q, const int32_t* seq_slot, int nseq,
+                                int max_qlen, int max_kv_len, const int32_t* logit_rows, int n_logit_rows,
+                                float* logits_out, long long logits_ld, float* layer_out, void* stream);
+/* ms and launches by kernel class since the last read (nclass >= 8): 0 dense projections, 1 per-head latent products,
+ * 2 latent attention, 3 windowed attention, 4 recurrence, 5 feed-forward activation, 6 norms / rotations / cache
+ * append, 7 output head */
+ASD_API int asd_rivetar_profile_read(asd_rivetar_engine_t* e, float* ms_by_class, int* launches_by_class, int nclass);
+ASD_API int asd_rivetar_device_error(asd_rivetar_engine_t* e);
+
 #ifdef __cplusplus
 }
 #endif
