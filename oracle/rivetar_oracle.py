@@ -28,10 +28,6 @@ def offset_norm(x, weight, eps):
     return unit_rms(x, eps) * (1.0 + weight)
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def polynorm(z, coeff, eps):
     """a N(z) + b N(z^2) + c N(z^3) + e with N = division by the root mean square over the feed-forward axis"""
     a, b, c, e = [coeff[i] for i in range(4)]
@@ -78,6 +74,13 @@ def visible(i: int, j: int, size: Optional[int], keep_first: int) -> bool:
     return i - j < size or j < keep_first
 
 
+def visibility(positions, mask: Optional[dict]) -> torch.Tensor:
+    """[T, T] booleans: may the row's position look at the column's?"""
+    mask = mask or {}
+    pos = [int(p) for p in positions]
+    return torch.tensor([[visible(i, j, mask.get("size"), mask.get("keep_first", 0)) for j in pos] for i in pos])
+
+
 # ------------------------------------------------------------------------------------------------ mixers
 def latent_attention(h, positions, w: Dict[str, torch.Tensor], m: dict, eps: float):
     """Queries through a normed latent; keys and values rebuilt per head from a shared normed latent plus one rotated
@@ -94,14 +97,10 @@ def latent_attention(h, positions, w: Dict[str, torch.Tensor], m: dict, eps: flo
     k_rot = rotate_pairs(ckr[:, R:], positions, rot["dims"], rot["base"], layout)          # [T, dr], all heads
     k_plain = (c @ w["uk"].T).reshape(T, H, dn)
     v = (c @ w["uv"].T).reshape(T, H, dv)
-    mask = m.get("mask") or {}
-    out = torch.zeros(T, H, dv, dtype=h.dtype)
-    for i in range(T):
-        js = [j for j in range(T) if visible(int(positions[i]), int(positions[j]), mask.get("size"), mask.get("keep_first", 0))]
-        for hd in range(H):
-            s = torch.stack([(q_plain[i, hd] @ k_plain[j, hd] + q_rot[i, hd] @ k_rot[j]) * m["scale"] for j in js])
-            p = torch.softmax(s, 0)
-            out[i, hd] = sum(p[n] * v[j, hd] for n, j in enumerate(js))
+    see = visibility(positions, m.get("mask"))                                             # [T, T]
+    s = (torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihd,jd->hij", q_rot, k_rot)) * m["scale"]
+    p = torch.softmax(s.masked_fill(~see[None], -math.inf), -1)
+    out = torch.einsum("hij,jhd->ihd", p, v)
     return out.reshape(T, H * dv) @ w["o"].T
 
 
@@ -135,17 +134,14 @@ def windowed_attention(h, positions, w: Dict[str, torch.Tensor], m: dict):
     q = rotate_pairs((h @ w["q"].T).reshape(T, H, dk), positions, rot["dims"], rot["base"], layout)
     k = rotate_pairs((h @ w["k"].T).reshape(T, G, dk), positions, rot["dims"], rot["base"], layout)
     v = rotate_pairs((h @ w["v"].T).reshape(T, G, dv), positions, dv, rot["base"], layout)
-    mask = m.get("mask") or {}
-    out = torch.zeros(T, H, dv, dtype=h.dtype)
-    for i in range(T):
-        js = [j for j in range(T) if visible(int(positions[i]), int(positions[j]), mask.get("size"), mask.get("keep_first", 0))]
-        for hd in range(H):
-            g = hd // (H // G)
-            s = torch.stack([(q[i, hd] @ k[j, g]) * m["scale"] for j in js])
-            top = torch.maximum(s.max(), w["sink"][hd])
-            e = torch.exp(s - top)
-            denom = e.sum() + torch.exp(w["sink"][hd] - top)
-            out[i, hd] = sum(e[n] / denom * v[j, g] for n, j in enumerate(js))
+    see = visibility(positions, m.get("mask"))
+    kv_of = torch.arange(H) // (H // G)                                                    # query head -> key/value head
+    s = torch.einsum("ihd,jhd->hij", q, k[:, kv_of]) * m["scale"]
+    s = s.masked_fill(~see[None], -math.inf)
+    # the sink is one more column of scores that carries no value
+    full = torch.cat([s, w["sink"].to(h.dtype)[:, None, None].expand(H, T, 1)], -1)
+    p = torch.softmax(full, -1)[..., :T]
+    out = torch.einsum("hij,jhd->ihd", p, v[:, kv_of])
     out = rotate_pairs(out, positions, dv, rot["base"], layout, sign=-1.0)
     return out.reshape(T, H * dv) @ w["o"].T
 
@@ -260,5 +256,5 @@ def random_model(cfg: dict, seed: int, scale: float = 1.0) -> Dict[str, torch.Te
             t = torch.randn(shape, generator=g) / float(cfg["embedding"]["scale"])
         else:
             t = torch.randn(shape, generator=g) * (scale / math.sqrt(shape[-1]))
-        w[name] = t
+        w[name] = t.to(torch.bfloat16)          # what a checkpoint stores
     return w
