@@ -306,6 +306,12 @@ static int forward(RvEngine* e, const Batch& b, const int* logit_rows, int n_row
     return 0;
 }
 
+// elements one execution's rows take in the pool, rounded up so that every execution starts on a 16-byte boundary
+static size_t pool_elems(const RvEngine* e, const RvRun& r, int num_pages) {
+    const size_t n = (size_t)num_pages * e->c.page_size * e->layers[r.layer].cache_row;
+    return (n + 7) & ~(size_t)7;
+}
+
 static const char* const kLayerNames[] = {"norm1", "norm1b", "norm2", "norm2b", "w_up", "w_down", "act", "w_o", "w_in",
                                           "q_norm", "kv_norm", "w_uq", "w_uk", "w_uv", "w_decay", "b_decay", "out_norm",
                                           "sink"};
@@ -452,7 +458,7 @@ size_t asd_rivetar_cache_bytes(const asd_rivetar_engine_t* h, int num_pages) {
     const RvEngine* e = static_cast<const RvEngine*>(h);
     if (!e) return 0;
     size_t n = 0;
-    for (const RvRun& r : e->runs) n += (size_t)num_pages * e->c.page_size * e->layers[r.layer].cache_row;
+    for (const RvRun& r : e->runs) n += pool_elems(e, r, num_pages);
     return n * e->esz;
 }
 
@@ -476,7 +482,7 @@ int asd_rivetar_set_cache(asd_rivetar_engine_t* h, void* pool, int num_pages, co
     for (RvRun& r : e->runs) {
         r.cache_off = off;
         r.state_off = soff;
-        off += (size_t)num_pages * e->c.page_size * e->layers[r.layer].cache_row;
+        off += pool_elems(e, r, num_pages);
         soff += (size_t)max_seqs * e->c.ring * e->layers[r.layer].state_elems;
     }
     return 0;

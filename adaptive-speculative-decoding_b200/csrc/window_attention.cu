@@ -7,11 +7,16 @@
 //   behind the tile; each pair masks per key.  Lane j scores key j (fp32 dot over dk), the warp keeps a running maximum
 //   and sum (online softmax) and lane l accumulates the value columns l, l + 32, ...  The sink enters the denominator
 //   once, at the end; the result is turned back by the query's position and stored in the engine's element type.
+// window_attn_mma: the same on the tensor cores for bf16 cache rows (mma.sync m16n8k16, fp32 accumulation).  One CTA of
+//   four warps per (64 query rows = tokens x query heads of one key/value head); tiles of 64 keys and values arrive by
+//   cp.async, two in flight.  The fp32 queries and the fp32 softmax weights enter the products as the sum of two bf16
+//   terms each, so scores and weights keep fp32 accuracy; maxima, sums and the sink are fp32.
 #include <cuda_bf16.h>
 
 #include "asd_internal.h"
 #include "blocks.h"
 #include "elem.cuh"
+#include "mma_sync.cuh"
 
 namespace asd {
 
@@ -206,6 +211,255 @@ int launch_simple(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int 
     return 0;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-core form.  Row r of the CTA's 64 is (token r / group, query head r % group of key/value head g).
+constexpr int WM_ROWS = 64, WM_KEYS = 64;
+
+__device__ __forceinline__ void split2(float x, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+    hi = __float2bfloat16(x);
+    lo = __float2bfloat16(x - __bfloat162float(hi));
+}
+
+template <int NV>   // value column tiles of 8: dv <= 8 * NV
+__global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* cu_q, const int* seq_slot, int TQ,
+                                                       const float* q, long long ldq, WindowDims d, const float* sink,
+                                                       const float* freq_v, PagedRows cache, void* out, int of32) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int LDQ = d.dk + 8, LDV = d.dv + 8;   // bf16 elements; 16 bytes of padding keep ldmatrix rows on distinct banks
+    __nv_bfloat16* Qh = reinterpret_cast<__nv_bfloat16*>(smraw);   // [64][LDQ]
+    __nv_bfloat16* Ql = Qh + WM_ROWS * LDQ;
+    __nv_bfloat16* Ks = Ql + WM_ROWS * LDQ;                        // [2][64][LDQ]
+    __nv_bfloat16* Vs = Ks + 2 * WM_KEYS * LDQ;                    // [2][64][LDV]
+    float* stage = reinterpret_cast<float*>(Ks);                   // [64][dv] once the last tile is consumed
+    const int group = d.heads / d.kv_heads;
+    const int seq = blockIdx.y, g = blockIdx.z;
+    const int t0 = cu_q[seq] + blockIdx.x * TQ, t_end = cu_q[seq + 1];
+    if (t0 >= t_end) return;
+    const int slot = seq_slot[seq];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_tok = min(TQ, t_end - t0), n_rows = n_tok * group;
+    const int p_first = ix.positions[t0], p_last = p_first + n_tok - 1;
+    int lo = p_first - d.window + 1;
+    if (lo < 0) lo = 0;
+    const int first_end = d.keep_first < lo ? d.keep_first : lo;
+    const int nA = (first_end + WM_KEYS - 1) / WM_KEYS, nB = (p_last + 1 - lo + WM_KEYS - 1) / WM_KEYS;
+    const int ntiles = nA + nB;
+    // queries as hi + lo bf16 terms
+    for (int i = tid; i < WM_ROWS * d.dk; i += 128) {
+        const int r = i / d.dk, c = i % d.dk;
+        float v = 0.f;
+        if (r < n_rows) v = q[(long long)(t0 + r / group) * ldq + (long long)(g * group + r % group) * d.dk + c];
+        __nv_bfloat16 hi, lw;
+        split2(v, hi, lw);
+        Qh[r * LDQ + c] = hi;
+        Ql[r * LDQ + c] = lw;
+    }
+    const __nv_bfloat16* pool = reinterpret_cast<const __nv_bfloat16*>(cache.pool);
+    const int nk = d.kv_heads * d.dk, rowlen = nk + d.kv_heads * d.dv;
+    const int ck = d.dk >> 3, cpr = (d.dk + d.dv) >> 3;
+    auto tile_range = [&](int i, int& j0, int& j_end) {
+        if (i < nA) {
+            j0 = i * WM_KEYS;
+            j_end = first_end;
+        } else {
+            j0 = lo + (i - nA) * WM_KEYS;
+            j_end = p_last + 1;
+        }
+    };
+    auto load_tile = [&](int buf, int i) {
+        int j0, j_end;
+        tile_range(i, j0, j_end);
+        __nv_bfloat16* kd = Ks + buf * WM_KEYS * LDQ;
+        __nv_bfloat16* vd = Vs + buf * WM_KEYS * LDV;
+        for (int c = tid; c < WM_KEYS * cpr; c += 128) {
+            const int r = c / cpr, cc = c % cpr;
+            const int kp = j0 + r;
+            const bool ok = kp < j_end;
+            const long long row = wcache_row(cache, slot, ok ? kp : j_end - 1) * rowlen;
+            if (cc < ck)
+                cp_async16((uint32_t)__cvta_generic_to_shared(kd + r * LDQ + cc * 8), pool + row + (long long)g * d.dk + cc * 8, ok);
+            else
+                cp_async16((uint32_t)__cvta_generic_to_shared(vd + r * LDV + (cc - ck) * 8),
+                           pool + row + nk + (long long)g * d.dv + (cc - ck) * 8, ok);
+        }
+    };
+    const int rA = warp * 16 + (lane >> 2), rB = rA + 8;
+    const bool okA = rA < n_rows, okB = rB < n_rows;
+    const int pA = p_first + rA / group, pB = p_first + rB / group;
+    const bool warp_live = warp * 16 < n_rows;
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+    float o[NV][4];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    const int nvt = d.dv >> 3;
+    load_tile(0, 0);
+    cp_async_commit();
+    for (int it = 0; it < ntiles; ++it) {
+        if (it + 1 < ntiles) {
+            load_tile((it + 1) & 1, it + 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();   // tile `it` has landed for every thread (and the queries are in place)
+        if (warp_live) {
+            int j0, j_end;
+            tile_range(it, j0, j_end);
+            const __nv_bfloat16* kb = Ks + (it & 1) * WM_KEYS * LDQ;
+            const __nv_bfloat16* vb = Vs + (it & 1) * WM_KEYS * LDV;
+            float s[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+            for (int ks = 0; ks < d.dk; ks += 16) {
+                uint32_t ah[4], al[4];
+                const int qoff = (warp * 16 + (lane & 15)) * LDQ + ks + (lane >> 4) * 8;
+                ldsm_x4((uint32_t)__cvta_generic_to_shared(Qh + qoff), ah);
+                ldsm_x4((uint32_t)__cvta_generic_to_shared(Ql + qoff), al);
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    uint32_t b[4];
+                    ldsm_x4((uint32_t)__cvta_generic_to_shared(kb + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LDQ + ks +
+                                                                ((lane >> 3) & 1) * 8), b);
+                    mma_bf16(s[2 * np], ah, b[0], b[1]);
+                    mma_bf16(s[2 * np], al, b[0], b[1]);
+                    mma_bf16(s[2 * np + 1], ah, b[2], b[3]);
+                    mma_bf16(s[2 * np + 1], al, b[2], b[3]);
+                }
+            }
+            // mask, running maxima
+            float txA = -INFINITY, txB = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int kp = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const int p = e < 2 ? pA : pB;
+                    const bool seen = (e < 2 ? okA : okB) && kp < j_end && kp <= p && (p - kp < d.window || kp < d.keep_first);
+                    const float v = seen ? s[nt][e] * d.scale : -INFINITY;
+                    s[nt][e] = v;
+                    if (e < 2)
+                        txA = fmaxf(txA, v);
+                    else
+                        txB = fmaxf(txB, v);
+                }
+            }
+            txA = fmaxf(txA, __shfl_xor_sync(0xffffffffu, txA, 1));
+            txA = fmaxf(txA, __shfl_xor_sync(0xffffffffu, txA, 2));
+            txB = fmaxf(txB, __shfl_xor_sync(0xffffffffu, txB, 1));
+            txB = fmaxf(txB, __shfl_xor_sync(0xffffffffu, txB, 2));
+            const float nA_ = fmaxf(mA, txA), nB_ = fmaxf(mB, txB);
+            const float sA = nA_ == -INFINITY ? 0.f : nA_, sB = nB_ == -INFINITY ? 0.f : nB_;   // nothing seen yet: weights 0
+            const float cA = expf(mA - sA), cB = expf(mB - sB);
+            mA = nA_, mB = nB_;
+            float sumA = 0.f, sumB = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                s[nt][0] = expf(s[nt][0] - sA);
+                s[nt][1] = expf(s[nt][1] - sA);
+                s[nt][2] = expf(s[nt][2] - sB);
+                s[nt][3] = expf(s[nt][3] - sB);
+                sumA += s[nt][0] + s[nt][1];
+                sumB += s[nt][2] + s[nt][3];
+            }
+            lA = lA * cA + sumA;
+            lB = lB * cB + sumB;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                o[i][0] *= cA, o[i][1] *= cA;
+                o[i][2] *= cB, o[i][3] *= cB;
+            }
+            // weights x values: 16 keys at a time, the weights as hi + lo bf16 terms
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t ph[4], pl[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float x0 = s[2 * j + (u >> 1)][(u & 1) * 2], x1 = s[2 * j + (u >> 1)][(u & 1) * 2 + 1];
+                    __nv_bfloat16 h0, l0, h1, l1;
+                    split2(x0, h0, l0);
+                    split2(x1, h1, l1);
+                    __nv_bfloat162 hh = __halves2bfloat162(h0, h1), ll = __halves2bfloat162(l0, l1);
+                    ph[u] = *reinterpret_cast<uint32_t*>(&hh);
+                    pl[u] = *reinterpret_cast<uint32_t*>(&ll);
+                }
+#pragma unroll
+                for (int vp = 0; vp < NV / 2; ++vp) {
+                    if (2 * vp < nvt) {
+                        uint32_t b[4];
+                        ldsm_x4_t((uint32_t)__cvta_generic_to_shared(vb + (j * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV +
+                                                                      (2 * vp + (lane >> 4)) * 8), b);
+                        mma_bf16(o[2 * vp], ph, b[0], b[1]);
+                        mma_bf16(o[2 * vp], pl, b[0], b[1]);
+                        mma_bf16(o[2 * vp + 1], ph, b[2], b[3]);
+                        mma_bf16(o[2 * vp + 1], pl, b[2], b[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();   // tile `it` is consumed: its buffer may be refilled (and, after the last tile, reused as staging)
+    }
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+    lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    float invA = 1.f / lA, invB = 1.f / lB;
+    if (sink) {   // one more term of the denominator, without a value
+        if (okA) {
+            const float sk = sink[g * group + rA % group], mf = fmaxf(mA, sk), so = expf(mA - mf);
+            invA = so / (lA * so + expf(sk - mf));
+        }
+        if (okB) {
+            const float sk = sink[g * group + rB % group], mf = fmaxf(mB, sk), so = expf(mB - mf);
+            invB = so / (lB * so + expf(sk - mf));
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (i < nvt) {
+            const int c = i * 8 + (lane & 3) * 2;
+            if (okA) stage[rA * d.dv + c] = o[i][0] * invA, stage[rA * d.dv + c + 1] = o[i][1] * invA;
+            if (okB) stage[rB * d.dv + c] = o[i][2] * invB, stage[rB * d.dv + c + 1] = o[i][3] * invB;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < n_rows * d.dv; i += 128) {
+        const int r = i / d.dv, c = i % d.dv;
+        const long long m = t0 + r / group;
+        stx(out, (m * d.heads + g * group + r % group) * d.dv + c, of32,
+            turned(stage + r * d.dv, c, d.dv, d.interleaved, (float)(p_first + r / group), freq_v, -1.f));
+    }
+}
+
+bool mma_supports(const WindowDims& d, const PagedRows& cache) {
+    const int group = d.heads / d.kv_heads;
+    return !cache.f32 && (d.dk % 16) == 0 && (d.dv % 16) == 0 && d.dv <= 128 && d.dk <= 256 && group <= WM_ROWS &&
+           (reinterpret_cast<uintptr_t>(cache.pool) & 15) == 0;
+}
+
+int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, const float* q,
+               long long ldq, const WindowDims& d, const float* sink, const float* freq_v, const PagedRows& cache, void* out,
+               int of32, cudaStream_t stream) {
+    const int group = d.heads / d.kv_heads;
+    const int TQ = WM_ROWS / group;
+    const size_t smem = (size_t)(2 * WM_ROWS * (d.dk + 8) + 2 * WM_KEYS * (d.dk + 8) + 2 * WM_KEYS * (d.dv + 8)) * 2;
+    dim3 grid((max_qlen + TQ - 1) / TQ, nseq, d.kv_heads);
+    if (grid.y > 65535 || grid.z > 65535) return set_error("windowed attention: too many sequences or heads");
+#define ASD_WM_CASE(N)                                                                                               \
+    {                                                                                                                \
+        auto fn = window_attn_mma<N>;                                                                                \
+        if (smem > 48 * 1024) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        fn<<<grid, 128, smem, stream>>>(ix, cu_q, seq_slot, TQ, q, ldq, d, sink, freq_v, cache, out, of32);          \
+    }
+    if (d.dv <= 32) ASD_WM_CASE(4)
+    else if (d.dv <= 64) ASD_WM_CASE(8)
+    else ASD_WM_CASE(16)
+#undef ASD_WM_CASE
+    count_launch(1);
+    ASD_CUDA(cudaGetLastError());
+    return 0;
+}
+
 int check_dims(const WindowDims& d) {
     if (d.heads <= 0 || d.kv_heads <= 0 || d.heads % d.kv_heads || d.dk <= 0 || d.dv <= 0 || (d.dv & 1) ||
         d.rot_dims < 0 || d.rot_dims > d.dk || (d.rot_dims & 1) || d.window <= 0 || d.keep_first < 0)
@@ -237,7 +491,8 @@ int launch_window_attention(const SeqIndex& ix, const int* cu_q, const int* seq_
     if (ix.M <= 0 || nseq <= 0) return 0;
     if (check_dims(d)) return -1;
     (void)max_kv_len;
-    (void)tiled;
+    if (tiled && mma_supports(d, cache))
+        return launch_mma(ix, cu_q, seq_slot, nseq, max_qlen, q, ldq, d, sink, freq_v, cache, out, of32, stream);
     return cache.f32 ? launch_simple<float>(ix, cu_q, seq_slot, nseq, max_qlen, q, ldq, d, sink, freq_v, cache, out, of32, stream)
                      : launch_simple<__nv_bfloat16>(ix, cu_q, seq_slot, nseq, max_qlen, q, ldq, d, sink, freq_v, cache, out, of32, stream);
 }

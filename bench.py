@@ -670,30 +670,81 @@ def run_ours(args):
         sys.exit(3)
 
 
-def family_sizes():
-    """(label, Mezilix config, Qwen2 config of the same width, depth, head count and active weights per layer)"""
-    from asd_b200.models.mezilix import sized_config
+def family_sizes(family="mezilix"):
+    """(label, configuration of the family, Qwen2 config of the same width, depth, head count and active weights per layer)"""
     from asd_b200.models.qwen2 import Qwen2Config
     out = []
     for label, width, heads, layers in (("w2048", 2048, 16, 4), ("w4096", 4096, 32, 4)):
-        mz = sized_config(width, layers, heads, vocab=32768, dim=128, rot_dim=64, kv_rank=512, window=4096, experts=8,
-                          top=2, ff=width, name=f"mezilix-{label}")
-        l = mz.layers[0]
-        active = (l.q_rows + l.cache_row) * width + l.heads * (l.dim + l.vdim) * l.kv_rank + width * l.heads * l.vdim \
-            + l.top * 2 * l.ff * width
+        if family == "rivetar":
+            from asd_b200.models import rivetar
+            layers = 6          # two of every mixer: latent attention, gated linear attention, windowed attention
+            fm = rivetar.sized_config(width, layers, heads, vocab=32768, dim=128, window=1024, keep_first=4, ff=3 * width,
+                                      name=f"rivetar-{label}")
+            shapes = rivetar.tensor_shapes(fm)
+            active = sum(a * b for k, (a, *r) in shapes.items() for b in r[:1] if k.startswith("l") and len(r) == 1) // layers
+        else:
+            from asd_b200.models.mezilix import sized_config
+            fm = sized_config(width, layers, heads, vocab=32768, dim=128, rot_dim=64, kv_rank=512, window=4096, experts=8,
+                              top=2, ff=width, name=f"mezilix-{label}")
+            l = fm.layers[0]
+            active = (l.q_rows + l.cache_row) * width + l.heads * (l.dim + l.vdim) * l.kv_rank + width * l.heads * l.vdim \
+                + l.top * 2 * l.ff * width
         kv = max(1, heads // 8)
         attn = (heads + 2 * kv) * 128 * width + heads * 128 * width
         inter = max(256, int(round((active - attn) / (3 * width) / 256)) * 256)
         qw = Qwen2Config(width, layers, heads, kv, inter, 32768, name=f"qwen2-{label}")
-        out.append((label, mz, qw))
+        out.append((label, fm, qw))
     return out
+
+
+def rivetar_model(cfg, M, kv_len, nseq):
+    """algorithmic (FLOPs, bytes) of one forward per kernel class, summed over the layer executions (bf16 engine)"""
+    D = cfg.width
+    tri = 0.5 if M > nseq else 1.0          # a prompt from an empty cache sees half of the keys on average
+    cls = {k: [0.0, 0.0] for k in ("dense", "head_products", "latent_attention", "window_attention", "recurrence")}
+
+    def add(k, fl, by):
+        cls[k][0] += fl
+        cls[k][1] += by
+    for i, _ in cfg.runs():
+        l = cfg.layers[i]
+        hv = l.heads * l.vdim
+        if l.type == "latent_attention":
+            rw, nq = l.kv_rank + l.rot_dim, l.heads * (l.dim + l.rot_dim)
+            n_in = l.q_rank + rw
+            wd = n_in * D + nq * l.q_rank
+            add("dense", 2.0 * M * wd, 2.0 * wd + M * (2 * D + 4 * n_in + 2 * l.q_rank + 4 * nq))
+            wh = l.heads * (l.dim + l.vdim) * l.kv_rank
+            add("head_products", 2.0 * M * wh, 2.0 * wh + 4.0 * M * l.heads * (l.dim + rw + l.kv_rank) + 2.0 * M * hv)
+            keys = min(l.window, kv_len)
+            add("latent_attention", 2.0 * M * l.heads * keys * (rw + l.kv_rank) * tri,
+                2.0 * nseq * keys * rw + 4.0 * M * l.heads * (rw + l.kv_rank))
+        elif l.type == "gla":
+            n_in = 2 * l.heads * l.dim + 2 * hv + l.decay_rank
+            add("dense", 2.0 * M * n_in * D, 2.0 * n_in * D + M * (2 * D + 4 * n_in))
+            add("recurrence", 4.0 * M * l.heads * l.dim * l.vdim,
+                8.0 * nseq * l.heads * l.dim * l.vdim + 4.0 * M * (3 * l.heads * l.dim + 2 * hv))
+        else:
+            kvw = l.kv_heads * (l.dim + l.vdim)
+            n_in = l.heads * l.dim + kvw
+            add("dense", 2.0 * M * n_in * D, 2.0 * n_in * D + M * (2 * D + 4 * n_in))
+            keys = min(l.window + l.keep_first, kv_len)
+            add("window_attention", 2.0 * M * l.heads * keys * (l.dim + l.vdim) * (tri if kv_len <= l.window else 1.0),
+                2.0 * nseq * (kv_len if M > nseq else keys) * kvw + 4.0 * M * l.heads * l.dim + 2.0 * M * hv)
+        wo = D * hv + 2 * l.ff * D
+        add("dense", 2.0 * M * wo, 2.0 * wo + M * (2 * hv + 4 * D + (2 * D + 4 * l.ff + 2 * l.ff + 4 * D if l.ff else 0)))
+    return {k: tuple(v) for k, v in cls.items()}
 
 
 def family_model(cfg, M, kv_len, nseq, peaks):
     """algorithmic FLOPs and bytes of one forward of M tokens (nseq sequences, kv_len keys each) per kernel class"""
     import math
     L = cfg.num_hidden_layers
-    if getattr(cfg, "architecture", None) == "Mezilix":
+    if getattr(cfg, "architecture", None) == "Rivetar":
+        L = 1           # rivetar_model already sums over the layer executions
+        cls = rivetar_model(cfg, M, kv_len, nseq)
+        head = (2.0 * nseq * cfg.vocab_size * cfg.width, 2.0 * cfg.vocab_size * cfg.width)
+    elif getattr(cfg, "architecture", None) == "Mezilix":
         l, D = cfg.layers[0], cfg.width
         nqd, rw = l.q_rows + l.cache_row, l.cache_row
         keys = min(l.window, kv_len)
@@ -722,13 +773,14 @@ def family_model(cfg, M, kv_len, nseq, peaks):
 
 
 def run_family(args):
-    """--family mezilix: prefill and decode throughput of the Mezilix engine at layer sizes of real models, beside the
+    """--family mezilix | rivetar: prefill and decode throughput of that family's engine at layer sizes of real models, beside the
     Qwen2 engine at the same width, depth, head count and active weights per layer (random weights, synthetic tokens).
     Per kernel class: device time (CUDA events around every launch) against its floor = max(FLOPs / measured cuBLAS bf16
     rate, bytes / measured copy bandwidth).  Prints one JSON object; the default workload of this file is untouched."""
     import torch
     import asd_b200  # noqa: F401
-    from asd_b200.engine import MezilixEngine, QwenEngine
+    from asd_b200.engine import MezilixEngine, QwenEngine, RivetarEngine
+    engines = {"mezilix": MezilixEngine, "rivetar": RivetarEngine, "qwen2": QwenEngine}
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     peaks = json.load(open(path)) if os.path.exists(path) else {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
     dev = torch.device("cuda", 0)
@@ -738,11 +790,16 @@ def run_family(args):
     clocks.start()
     records = []
     ctx, pre_len = args.prefix if args.prefix != 512 else 2048, 1024
-    for label, mz_cfg, qw_cfg in family_sizes():
-        for fam, cfg in (("mezilix", mz_cfg), ("qwen2", qw_cfg)):
+    only = {o.split("=", 1)[1] for o in (args.opt or []) if o.startswith("only=")}      # --opt only=rivetar / only=w2048
+    for label, mz_cfg, qw_cfg in family_sizes(args.family):
+        if only & {"w2048", "w4096"} and label not in only:
+            continue
+        for fam, cfg in ((args.family, mz_cfg), ("qwen2", qw_cfg)):
+            if only & set(engines) and fam not in only:
+                continue
             B = max(args.batch, 64)
             kw = dict(max_seqs=B, max_seq_len=ctx + 64, max_tokens=4096, device=dev)
-            eng = (MezilixEngine(cfg, **kw) if fam == "mezilix" else QwenEngine(cfg, **kw)).load_random(seed=3)
+            eng = engines[fam](cfg, **kw).load_random(seed=3)
             g = torch.Generator().manual_seed(5)
             rec = {"size": label, "family": fam, "model": cfg.name, "params_per_layer_active_M": None, "runs": []}
 
@@ -823,7 +880,7 @@ def main():
     ap.add_argument("--no-fuse-norm", action="store_true", help="separate add+RMSNorm kernels instead of the fused epilogues")
     ap.add_argument("--nccl-only", action="store_true", help="TP boundaries through ncclAllReduce instead of the fused kernel")
     ap.add_argument("--opt", action="append", help="engine option name=value (e.g. pdl=0, attn_impl=0)")
-    ap.add_argument("--family", default=None, choices=["mezilix"],
+    ap.add_argument("--family", default=None, choices=["mezilix", "rivetar"],
                     help="instead of the default workload: prefill / decode throughput of this model family beside Qwen2 at equal size")
     args = ap.parse_args()
     if args.warmup < 3:

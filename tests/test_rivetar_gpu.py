@@ -368,6 +368,30 @@ def test_far_key_among_hundreds_in_causal_latent_attention():
         close(eng)
 
 
+def test_both_windowed_attention_kernels_agree():
+    """bf16 cache rows: the tensor-core kernel (queries and weights as two bf16 terms) and the one-warp-per-pair kernel
+    read the same cache, so they differ by fp32 roundings only; both stay within bf16's reach of the oracle.  Group sizes
+    that do and do not divide the row tile, value sizes up to the kernel's limit, prompts, portions and single tokens"""
+    for heads, kv_heads, dim, vdim, size, keep in ((4, 4, 32, 16, 100, 5), (6, 2, 16, 48, 37, 0), (8, 1, 64, 128, 130, 70),
+                                                   (5, 1, 48, 32, 1000, 3)):
+        cfg = config([window(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, size=size, keep_first=keep, rot_dims=16,
+                             scale=0.3, ff=0)])
+        w = O.random_model(cfg, seed=41)
+        w["l0.mix.sink"] = torch.linspace(-2.0, 4.0, heads)
+        ids = tokens(330, 96, 42)
+        ref, _ = O.forward(cfg, w, ids)
+        for cuts in ([330], [200, 64, 1, 1, 1, 2, 61], [300] + [1] * 30):
+            got = []
+            for fused in (1, 0):
+                eng = make_engine(cfg, w, dtype=torch.bfloat16, max_tokens=512, max_seq_len=512, page_size=8)
+                eng.set_option("fused_attn", fused)
+                slot = eng.open_sequence()
+                got.append(feed(eng, slot, ids, cuts))
+                close(eng)
+                assert rel_err(got[-1], ref)[0] < 5e-2, (heads, kv_heads, cuts, fused)
+            assert rel_err(got[0], got[1].cpu())[0] < 2e-3, (heads, kv_heads, cuts)
+
+
 # ------------------------------------------------------------------------------------------------ bf16 engine
 @pytest.mark.parametrize("tc", [1, 0], ids=["tcgen05", "cuda-cores"])
 @pytest.mark.parametrize("cfg_dict", [SMALL, ODD], ids=["small", "odd"])
