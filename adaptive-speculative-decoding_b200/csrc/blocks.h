@@ -189,7 +189,7 @@ struct GlaDims {
     int heads, dk, dv;
     int low;        // inner size of the decay projection
     float tau;
-    float q_scale;  // applied to q inside the recurrence
+    float q_scale;  // scale of the queries (applied to the result, which is linear in q)
 };
 // alpha[m][heads * dk] = exp(log_sigmoid(w_decay . a[m] + b_decay) / tau); a = fp32 rows of `low` floats lda apart
 int launch_gla_decay(const float* a, long long lda, const float* w_decay, const float* b_decay, const GlaDims& d,

@@ -1,11 +1,11 @@
 // Gated linear attention: a recurrence with a [dk][dv] state per head and a decay per key channel,
 //   S_t = diag(alpha_t) S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t,   alpha_t = sigmoid(z_t)^(1 / tau).
-// gla_decay_kernel:  alpha from the inner decay projection (one thread per channel, fp32).
+// gla_decay_kernel:  alpha from the inner decay projection (one thread per channel and 32 tokens, fp32).
 // gla_recurrence_kernel: one CTA per (sequence, head, 32 value columns).  Columns of S never mix, so a CTA owns its
-//   columns for the whole run of new positions: lane = column, warp = a slice of RS = ceil(dk / 32) consecutive key
-//   rows' worth of state held in registers.  The new positions are staged CH at a time in shared memory (q, k, alpha
-//   rows and the CTA's 32 value columns); per position every thread updates its rows and forms its slice's part of
-//   o, and after the chunk the slices are added in index order.  The arithmetic per position is the same whatever the
+//   columns for the whole run of new positions: lane = column, warp = a slice of 4 to 32 consecutive key rows' worth of
+//   state held in registers (up to eight warps).  The new positions are staged CH at a time in shared memory (q, k,
+//   decay rows and the CTA's 32 value columns) by cp.async, one chunk ahead; per position every thread
+//   updates its rows and forms its slice's part of o, and after the chunk the slices are added in index order.  The arithmetic per position is the same whatever the
 //   chunking or the batch, so a sequence's outputs do not depend on how its tokens were cut into forwards.
 //   The state lives in fp32 [slot][ring][head][dk][dv]; entry p % ring is the state after position p.
 // gla_out_kernel: RMS norm of every head's o over dv (plain weight), times silu(gate).
@@ -22,104 +22,164 @@ namespace {
 constexpr int GLA_CH = 16;   // positions staged per chunk
 constexpr int GLA_NR = 32;   // state rows per thread at most
 
-__global__ void gla_decay_kernel(const float* a, long long lda, const float* w_decay, const float* b_decay, GlaDims d,
-                                 float* alpha) {
-    extern __shared__ float av[];   // [low]
-    const int m = blockIdx.x, n = d.heads * d.dk;
-    for (int r = threadIdx.x; r < d.low; r += blockDim.x) av[r] = a[(long long)m * lda + r];
+__device__ __forceinline__ void cp_async4(float* dst, const float* src, bool valid) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(dst);
+    const int sz = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(addr), "l"(src), "r"(sz) : "memory");
+}
+
+constexpr int GD_TOK = 32, GD_CH = 256;   // tokens x channels per CTA of the decay kernel
+
+// One CTA = 256 channels x 32 tokens: the channels' projection rows are staged transposed ([low][256], so that the
+// threads of a warp read consecutive words) and reused for all the tile's tokens, whose inner vectors every thread
+// reads as broadcasts.
+__global__ void __launch_bounds__(GD_CH) gla_decay_kernel(const float* a, long long lda, const float* w_decay,
+                                                          const float* b_decay, GlaDims d, float* alpha, int M) {
+    extern __shared__ float sm[];
+    float* wT = sm;                      // [low][GD_CH]
+    float* av = sm + d.low * GD_CH;      // [GD_TOK][low]
+    const int n = d.heads * d.dk;
+    const int c0 = blockIdx.x * GD_CH, m0 = blockIdx.y * GD_TOK;
+    const int nt = min(GD_TOK, M - m0);
+    for (int i = threadIdx.x; i < GD_CH * d.low; i += GD_CH) {
+        const int c = i / d.low, r = i - c * d.low;
+        wT[r * GD_CH + c] = c0 + c < n ? w_decay[(long long)(c0 + c) * d.low + r] : 0.f;
+    }
+    for (int i = threadIdx.x; i < GD_TOK * d.low; i += GD_CH) {
+        const int t = i / d.low, r = i - t * d.low;
+        av[i] = t < nt ? a[(long long)(m0 + t) * lda + r] : 0.f;
+    }
     __syncthreads();
-    const float inv_tau = 1.f / d.tau;
-    for (int c = threadIdx.x; c < n; c += blockDim.x) {
-        const float* wr = w_decay + (long long)c * d.low;
-        float z = 0.f;
-        for (int r = 0; r < d.low; ++r) z = fmaf(wr[r], av[r], z);
-        z += b_decay[c];
-        // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
-        const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
-        alpha[(long long)m * n + c] = expf(ls * inv_tau);
+    const int c = c0 + threadIdx.x;
+    if (c >= n) return;
+    float z[GD_TOK];
+#pragma unroll
+    for (int t = 0; t < GD_TOK; ++t) z[t] = 0.f;
+    for (int r = 0; r < d.low; ++r) {
+        const float w = wT[r * GD_CH + threadIdx.x];
+#pragma unroll
+        for (int t = 0; t < GD_TOK; ++t) z[t] = fmaf(w, av[t * d.low + r], z[t]);
+    }
+    const float bias = b_decay[c], inv_tau = 1.f / d.tau;
+#pragma unroll
+    for (int t = 0; t < GD_TOK; ++t) {
+        if (t < nt) {
+            const float zz = z[t] + bias;
+            // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
+            const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));
+            alpha[(long long)(m0 + t) * n + c] = expf(ls * inv_tau);
+        }
     }
 }
 
-__global__ void __launch_bounds__(256) gla_recurrence_kernel(SeqIndex ix, const int* cu_q, const int* seq_slot,
-                                                             const float* q, const float* k, const float* v,
-                                                             long long ld, const float* alpha, GlaDims d, float* state,
-                                                             int ring, float* out) {
-    extern __shared__ float sm[];
+// ROWS state rows per thread (a multiple of 4: the staged q, k and decay rows are read as float4); the staged rows are
+// padded with zeros up to warps x ROWS, so rows beyond dk keep a zero state and add nothing.
+template <int ROWS>
+__global__ void __launch_bounds__(256, 2) gla_recurrence_kernel(SeqIndex ix, const int* cu_q, const int* seq_slot,
+                                                            const float* q, const float* k, const float* v, long long ld,
+                                                            const float* alpha, GlaDims d, float* state, int ring,
+                                                            float* out) {
+    extern __shared__ __align__(16) float sm[];
     const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * 32;
     const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
     if (t0 >= t1) return;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, RS = blockDim.x >> 5;
-    const int rows_per = (d.dk + RS - 1) / RS;          // <= GLA_NR
-    const int r0 = warp * rows_per;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, RS = blockDim.x >> 5, nthr = blockDim.x;
+    const int dkp = RS * ROWS;                          // padded key size
+    const int r0 = warp * ROWS;
     const int col = col0 + lane;
     const bool col_ok = col < d.dv;
     const int slot = seq_slot[seq];
     const int p0 = ix.positions[t0];
-    // shared: q, k, alpha [CH][dk] each, v [CH][32], partial o [RS][CH][32]
-    float* qs = sm;
-    float* ks = qs + GLA_CH * d.dk;
-    float* as = ks + GLA_CH * d.dk;
-    float* vs = as + GLA_CH * d.dk;
-    float* part = vs + GLA_CH * 32;
+    // shared: two buffers of { q, k, decay [CH][dkp] each, v [CH][32] }, then the partial o [RS][CH][32]
+    const int buf_elems = 3 * GLA_CH * dkp + GLA_CH * 32;
+    float* part = sm + 2 * buf_elems;
     const long long st_head = ((long long)head * d.dk) * d.dv;
     const long long st_entry = (long long)d.heads * d.dk * d.dv;
     float* st_slot = state + (long long)slot * ring * st_entry;
-    float S[GLA_NR];
+    float S[ROWS];
 #pragma unroll
-    for (int r = 0; r < GLA_NR; ++r) S[r] = 0.f;
+    for (int r = 0; r < ROWS; ++r) S[r] = 0.f;
     if (p0 > 0 && col_ok) {
         const float* src = st_slot + (long long)((p0 - 1) % ring) * st_entry + st_head;
 #pragma unroll
-        for (int r = 0; r < GLA_NR; ++r)
-            if (r < rows_per && r0 + r < d.dk) S[r] = src[(long long)(r0 + r) * d.dv + col];
+        for (int r = 0; r < ROWS; ++r)
+            if (r0 + r < d.dk) S[r] = src[(long long)(r0 + r) * d.dv + col];
     }
     const int hq = head * d.dk, hv = head * d.dv;
     const int n_alpha = d.heads * d.dk;
-    for (int c0 = t0; c0 < t1; c0 += GLA_CH) {
+    // a chunk's rows arrive by 4-byte cp.async (any alignment), one chunk ahead of the arithmetic; rows beyond the
+    // chunk's positions and key channels beyond dk are filled with zeros
+    auto fetch = [&](int buf, int c0) {
         const int nt = min(GLA_CH, t1 - c0);
-        __syncthreads();   // the previous chunk's partial sums have been read
-        for (int i = threadIdx.x; i < nt * d.dk; i += blockDim.x) {
-            const int t = i / d.dk, c = i % d.dk;
-            const long long row = (long long)(c0 + t) * ld;
-            qs[t * d.dk + c] = q[row + hq + c] * d.q_scale;
-            ks[t * d.dk + c] = k[row + hq + c];
-            as[t * d.dk + c] = alpha[(long long)(c0 + t) * n_alpha + hq + c];
+        float* qd = sm + buf * buf_elems;
+        float* kd = qd + GLA_CH * dkp;
+        float* ad = kd + GLA_CH * dkp;
+        float* vd = ad + GLA_CH * dkp;
+        for (int i = threadIdx.x; i < nt * dkp; i += nthr) {        // rows beyond the chunk's positions are never read
+            const int t = i / dkp, c = i - t * dkp;
+            const bool ok = c < d.dk;
+            const long long row = ok ? (long long)(c0 + t) * ld + hq + c : 0;
+            cp_async4(qd + i, q + row, ok);
+            cp_async4(kd + i, k + row, ok);
+            cp_async4(ad + i, alpha + (ok ? (long long)(c0 + t) * n_alpha + hq + c : 0), ok);
         }
-        for (int i = threadIdx.x; i < nt * 32; i += blockDim.x) {
+        for (int i = threadIdx.x; i < nt * 32; i += nthr) {
             const int t = i >> 5, c = i & 31;
-            vs[i] = col0 + c < d.dv ? v[(long long)(c0 + t) * ld + hv + col0 + c] : 0.f;
+            const bool ok = col0 + c < d.dv;
+            cp_async4(vd + i, v + (ok ? (long long)(c0 + t) * ld + hv + col0 + c : 0), ok);
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(0, t0);
+    int it = 0;
+    for (int c0 = t0; c0 < t1; c0 += GLA_CH, ++it) {
+        const int nt = min(GLA_CH, t1 - c0);
+        if (c0 + GLA_CH < t1) {
+            fetch((it + 1) & 1, c0 + GLA_CH);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();   // this chunk's rows have landed for every thread; the previous partial sums have been read
+        const float* qs = sm + (it & 1) * buf_elems;
+        const float* ks = qs + GLA_CH * dkp;
+        const float* as = ks + GLA_CH * dkp;
+        const float* vs = as + GLA_CH * dkp;
         for (int t = 0; t < nt; ++t) {
             const float vt = vs[t * 32 + lane];
-            const float* qt = qs + t * d.dk + r0;
-            const float* kt = ks + t * d.dk + r0;
-            const float* at = as + t * d.dk + r0;
-            float o = 0.f;
+            const float4* qt = reinterpret_cast<const float4*>(qs + t * dkp + r0);
+            const float4* kt = reinterpret_cast<const float4*>(ks + t * dkp + r0);
+            const float4* at = reinterpret_cast<const float4*>(as + t * dkp + r0);
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-            for (int r = 0; r < GLA_NR; ++r) {
-                if (r < rows_per && r0 + r < d.dk) {
-                    S[r] = fmaf(at[r], S[r], kt[r] * vt);
-                    o = fmaf(S[r], qt[r], o);
-                }
+            for (int r = 0; r < ROWS; r += 4) {
+                const float4 a4 = at[r >> 2], k4 = kt[r >> 2], q4 = qt[r >> 2];
+                S[r] = fmaf(a4.x, S[r], k4.x * vt);
+                S[r + 1] = fmaf(a4.y, S[r + 1], k4.y * vt);
+                S[r + 2] = fmaf(a4.z, S[r + 2], k4.z * vt);
+                S[r + 3] = fmaf(a4.w, S[r + 3], k4.w * vt);
+                o0 = fmaf(S[r], q4.x, o0);
+                o1 = fmaf(S[r + 1], q4.y, o1);
+                o2 = fmaf(S[r + 2], q4.z, o2);
+                o3 = fmaf(S[r + 3], q4.w, o3);
             }
-            part[(warp * GLA_CH + t) * 32 + lane] = o;
+            part[(warp * GLA_CH + t) * 32 + lane] = (o0 + o1) + (o2 + o3);
             // the last `ring` new positions leave their state behind
             const int m = c0 + t;
             if (t1 - m <= ring && col_ok) {
                 float* dst = st_slot + (long long)((p0 + (m - t0)) % ring) * st_entry + st_head;
 #pragma unroll
-                for (int r = 0; r < GLA_NR; ++r)
-                    if (r < rows_per && r0 + r < d.dk) dst[(long long)(r0 + r) * d.dv + col] = S[r];
+                for (int r = 0; r < ROWS; ++r)
+                    if (r0 + r < d.dk) dst[(long long)(r0 + r) * d.dv + col] = S[r];
             }
         }
-        __syncthreads();
-        for (int i = threadIdx.x; i < nt * 32; i += blockDim.x) {
+        __syncthreads();   // the chunk is consumed (its buffer may be refilled) and the partial sums are complete
+        for (int i = threadIdx.x; i < nt * 32; i += nthr) {
             const int t = i >> 5, c = i & 31;
             if (col0 + c >= d.dv) continue;
             float o = 0.f;
             for (int w = 0; w < RS; ++w) o += part[(w * GLA_CH + t) * 32 + c];
-            out[(long long)(c0 + t) * d.heads * d.dv + hv + col0 + c] = o;
+            out[(long long)(c0 + t) * d.heads * d.dv + hv + col0 + c] = o * d.q_scale;
         }
     }
 }
@@ -149,7 +209,13 @@ int launch_gla_decay(const float* a, long long lda, const float* w_decay, const 
                      float* alpha, int M, cudaStream_t stream) {
     if (M <= 0) return 0;
     if (d.low <= 0 || !(d.tau > 0.f)) return set_error("gla: decay projection of size %d, tau %f", d.low, d.tau);
-    gla_decay_kernel<<<M, 128, d.low * sizeof(float), stream>>>(a, lda, w_decay, b_decay, d, alpha);
+    const size_t smem = (size_t)d.low * (GD_CH + GD_TOK) * sizeof(float);
+    if (smem > 200 * 1024) return set_error("gla: decay projection of size %d does not fit shared memory", d.low);
+    if (smem > 48 * 1024)
+        ASD_CUDA(cudaFuncSetAttribute(gla_decay_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((d.heads * d.dk + GD_CH - 1) / GD_CH, (M + GD_TOK - 1) / GD_TOK);
+    if (grid.y > 65535) return set_error("gla: too many tokens");
+    gla_decay_kernel<<<grid, GD_CH, smem, stream>>>(a, lda, w_decay, b_decay, d, alpha, M);
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
     return 0;
@@ -161,13 +227,25 @@ int launch_gla_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_sl
     if (ix.M <= 0 || nseq <= 0) return 0;
     if (d.dk <= 0 || d.dk > 8 * GLA_NR) return set_error("gla: key size %d outside 1..%d", d.dk, 8 * GLA_NR);
     if (ring <= 0 || !state) return set_error("gla: no state");
-    const int RS = (d.dk + GLA_NR - 1) / GLA_NR;     // warps: slices of at most GLA_NR key rows
-    const size_t smem = (size_t)(3 * GLA_CH * d.dk + GLA_CH * 32 + RS * GLA_CH * 32) * sizeof(float);
-    if (smem > 48 * 1024)
-        ASD_CUDA(cudaFuncSetAttribute(gla_recurrence_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // the fewest state rows per thread (4, 8, 16 or 32) that at most eight warps cover
+    int rows = 4;
+    while (rows * 8 < d.dk) rows *= 2;
+    const int RS = (d.dk + rows - 1) / rows;
+    const int dkp = RS * rows;
+    const size_t smem = (size_t)(2 * (3 * GLA_CH * dkp + GLA_CH * 32) + RS * GLA_CH * 32) * sizeof(float);
     dim3 grid(nseq, d.heads, (d.dv + 31) / 32);
     if (grid.y > 65535 || grid.z > 65535) return set_error("gla: too many heads or value columns");
-    gla_recurrence_kernel<<<grid, RS * 32, smem, stream>>>(ix, cu_q, seq_slot, q, k, v, ld, alpha, d, state, ring, out);
+#define ASD_GLA_CASE(R)                                                                                               \
+    {                                                                                                                 \
+        auto fn = gla_recurrence_kernel<R>;                                                                           \
+        if (smem > 48 * 1024) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        fn<<<grid, RS * 32, smem, stream>>>(ix, cu_q, seq_slot, q, k, v, ld, alpha, d, state, ring, out);             \
+    }
+    if (rows == 4) ASD_GLA_CASE(4)
+    else if (rows == 8) ASD_GLA_CASE(8)
+    else if (rows == 16) ASD_GLA_CASE(16)
+    else ASD_GLA_CASE(32)
+#undef ASD_GLA_CASE
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
     return 0;

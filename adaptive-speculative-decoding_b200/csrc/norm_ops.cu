@@ -72,12 +72,16 @@ __global__ void rms_rows_kernel(const float* in, long long ld_in, const float* w
         stx(out, (long long)blockIdx.x * ld_out + i, of32, src[i] * r * (plus_one ? 1.f + w[i] : w[i]));
 }
 
-__global__ void polynorm_kernel(const float* z, const float* coeff, float eps, void* out, int of32, int F) {
-    __shared__ float red[33];
+// dynamic shared memory: the row (F floats, if it fits: `staged`) + 33 for the block sums
+__global__ void polynorm_kernel(const float* z, const float* coeff, float eps, void* out, int of32, int F, int staged) {
+    extern __shared__ float sm[];
+    float* red = sm;
+    float* row = sm + 33;
     const float* src = z + (long long)blockIdx.x * F;
     float s2 = 0.f, s4 = 0.f, s6 = 0.f;
     for (int i = threadIdx.x; i < F; i += blockDim.x) {
         const float v = src[i], v2 = v * v, v3 = v2 * v;
+        if (staged) row[i] = v;
         s2 += v2;
         s4 += v2 * v2;
         s6 += v3 * v3;
@@ -89,7 +93,7 @@ __global__ void polynorm_kernel(const float* z, const float* coeff, float eps, v
     const float a = coeff[0] / sqrtf(s2 * inv + eps), b = coeff[1] / sqrtf(s4 * inv + eps),
                 c = coeff[2] / sqrtf(s6 * inv + eps), e = coeff[3];
     for (int i = threadIdx.x; i < F; i += blockDim.x) {
-        const float v = src[i], v2 = v * v;
+        const float v = staged ? row[i] : src[i], v2 = v * v;
         stx(out, (long long)blockIdx.x * F + i, of32, a * v + b * v2 + c * (v2 * v) + e);
     }
 }
@@ -135,7 +139,11 @@ int launch_rms_rows(const float* in, long long ld_in, const float* w, int plus_o
 
 int launch_polynorm(const float* z, const float* coeff, float eps, void* out, int of32, int M, int F, cudaStream_t stream) {
     if (M <= 0 || F <= 0) return 0;
-    polynorm_kernel<<<M, row_threads(F), 0, stream>>>(z, coeff, eps, out, of32, F);
+    const int staged = (size_t)F * sizeof(float) <= 96 * 1024;
+    const size_t smem = (33 + (staged ? (size_t)F : 0)) * sizeof(float);
+    if (smem > 48 * 1024)
+        ASD_CUDA(cudaFuncSetAttribute(polynorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    polynorm_kernel<<<M, row_threads(F), smem, stream>>>(z, coeff, eps, out, of32, F, staged);
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
     return 0;

@@ -220,7 +220,9 @@ __device__ __forceinline__ void split2(float x, __nv_bfloat16& hi, __nv_bfloat16
     lo = __float2bfloat16(x - __bfloat162float(hi));
 }
 
-template <int NV>   // value column tiles of 8: dv <= 8 * NV
+// STAGES key/value tiles are in flight.  When the CTA has at most 16 rows (single-token steps), all four warps take
+// those rows and a quarter of every tile's keys each, and their partial results are merged at the end.
+template <int NV, int STAGES>   // value column tiles of 8: dv <= 8 * NV
 __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* cu_q, const int* seq_slot, int TQ,
                                                        const float* q, long long ldq, WindowDims d, const float* sink,
                                                        const float* freq_v, PagedRows cache, void* out, int of32) {
@@ -228,9 +230,10 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
     const int LDQ = d.dk + 8, LDV = d.dv + 8;   // bf16 elements; 16 bytes of padding keep ldmatrix rows on distinct banks
     __nv_bfloat16* Qh = reinterpret_cast<__nv_bfloat16*>(smraw);   // [64][LDQ]
     __nv_bfloat16* Ql = Qh + WM_ROWS * LDQ;
-    __nv_bfloat16* Ks = Ql + WM_ROWS * LDQ;                        // [2][64][LDQ]
-    __nv_bfloat16* Vs = Ks + 2 * WM_KEYS * LDQ;                    // [2][64][LDV]
+    __nv_bfloat16* Ks = Ql + WM_ROWS * LDQ;                        // [STAGES][64][LDQ]
+    __nv_bfloat16* Vs = Ks + STAGES * WM_KEYS * LDQ;               // [STAGES][64][LDV]
     float* stage = reinterpret_cast<float*>(Ks);                   // [64][dv] once the last tile is consumed
+    float* stage_ml = stage + WM_ROWS * d.dv;                      // [64][2]: maximum and sum of every warp's share
     const int group = d.heads / d.kv_heads;
     const int seq = blockIdx.y, g = blockIdx.z;
     const int t0 = cu_q[seq] + blockIdx.x * TQ, t_end = cu_q[seq + 1];
@@ -245,14 +248,15 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
     const int nA = (first_end + WM_KEYS - 1) / WM_KEYS, nB = (p_last + 1 - lo + WM_KEYS - 1) / WM_KEYS;
     const int ntiles = nA + nB;
     // queries as hi + lo bf16 terms
-    for (int i = tid; i < WM_ROWS * d.dk; i += 128) {
-        const int r = i / d.dk, c = i % d.dk;
-        float v = 0.f;
-        if (r < n_rows) v = q[(long long)(t0 + r / group) * ldq + (long long)(g * group + r % group) * d.dk + c];
-        __nv_bfloat16 hi, lw;
-        split2(v, hi, lw);
-        Qh[r * LDQ + c] = hi;
-        Ql[r * LDQ + c] = lw;
+    const int q_rows = n_rows <= 16 ? 16 : WM_ROWS;      // rows the products read (the rest of a single-token tile is unused)
+    for (int r = warp; r < q_rows; r += 4) {
+        const float* src = r < n_rows ? q + (long long)(t0 + r / group) * ldq + (long long)(g * group + r % group) * d.dk : nullptr;
+        for (int c = lane; c < d.dk; c += 32) {
+            __nv_bfloat16 hi, lw;
+            split2(src ? src[c] : 0.f, hi, lw);
+            Qh[r * LDQ + c] = hi;
+            Ql[r * LDQ + c] = lw;
+        }
     }
     const __nv_bfloat16* pool = reinterpret_cast<const __nv_bfloat16*>(cache.pool);
     const int nk = d.kv_heads * d.dk, rowlen = nk + d.kv_heads * d.dv;
@@ -266,58 +270,69 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             j_end = p_last + 1;
         }
     };
-    auto load_tile = [&](int buf, int i) {
+    // two threads per key row: one page lookup each (made a tile ahead of the copies that need it), then every other
+    // 16-byte chunk of the row's keys and values
+    auto lookup = [&](int i) -> long long {
+        if (i >= ntiles) return 0;
+        int j0, j_end;
+        tile_range(i, j0, j_end);
+        const int kp = j0 + (tid >> 1);
+        return wcache_row(cache, slot, kp < j_end ? kp : j_end - 1) * rowlen;
+    };
+    auto load_tile = [&](int buf, int i, long long row_off) {
         int j0, j_end;
         tile_range(i, j0, j_end);
         __nv_bfloat16* kd = Ks + buf * WM_KEYS * LDQ;
         __nv_bfloat16* vd = Vs + buf * WM_KEYS * LDV;
-        for (int c = tid; c < WM_KEYS * cpr; c += 128) {
-            const int r = c / cpr, cc = c % cpr;
-            const int kp = j0 + r;
-            const bool ok = kp < j_end;
-            const long long row = wcache_row(cache, slot, ok ? kp : j_end - 1) * rowlen;
-            if (cc < ck)
-                cp_async16((uint32_t)__cvta_generic_to_shared(kd + r * LDQ + cc * 8), pool + row + (long long)g * d.dk + cc * 8, ok);
-            else
-                cp_async16((uint32_t)__cvta_generic_to_shared(vd + r * LDV + (cc - ck) * 8),
-                           pool + row + nk + (long long)g * d.dv + (cc - ck) * 8, ok);
-        }
+        const int r = tid >> 1;
+        const bool ok = j0 + r < j_end;
+        const __nv_bfloat16* src = pool + row_off;
+        const __nv_bfloat16* ksrc = src + (long long)g * d.dk;
+        const __nv_bfloat16* vsrc = src + nk + (long long)g * d.dv;
+        for (int cc = tid & 1; cc < ck; cc += 2)
+            cp_async16((uint32_t)__cvta_generic_to_shared(kd + r * LDQ + cc * 8), ksrc + cc * 8, ok);
+        for (int cc = tid & 1; cc < cpr - ck; cc += 2)
+            cp_async16((uint32_t)__cvta_generic_to_shared(vd + r * LDV + cc * 8), vsrc + cc * 8, ok);
     };
-    const int rA = warp * 16 + (lane >> 2), rB = rA + 8;
+    const bool ksplit = n_rows <= 16;                     // every warp: rows 0 .. 15, keys [16 warp, 16 warp + 16) of a tile
+    const int row0 = ksplit ? 0 : warp * 16, key0 = ksplit ? warp * 16 : 0, npw = ksplit ? 1 : 4;
+    const int rA = row0 + (lane >> 2), rB = rA + 8;
     const bool okA = rA < n_rows, okB = rB < n_rows;
     const int pA = p_first + rA / group, pB = p_first + rB / group;
-    const bool warp_live = warp * 16 < n_rows;
+    const bool warp_live = row0 < n_rows;
     float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
     float o[NV][4];
 #pragma unroll
     for (int i = 0; i < NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     const int nvt = d.dv >> 3;
-    load_tile(0, 0);
-    cp_async_commit();
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) {
+        if (i < ntiles) load_tile(i, i, lookup(i));
+        cp_async_commit();
+    }
+    long long next_off = lookup(STAGES - 1);
     for (int it = 0; it < ntiles; ++it) {
-        if (it + 1 < ntiles) {
-            load_tile((it + 1) & 1, it + 1);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        if (it + STAGES - 1 < ntiles) load_tile((it + STAGES - 1) % STAGES, it + STAGES - 1, next_off);
+        cp_async_commit();                 // (an empty group keeps the count of groups in flight uniform)
+        next_off = lookup(it + STAGES);    // its latency passes behind this tile's arithmetic
+        cp_async_wait<STAGES - 1>();
         __syncthreads();   // tile `it` has landed for every thread (and the queries are in place)
         if (warp_live) {
             int j0, j_end;
             tile_range(it, j0, j_end);
-            const __nv_bfloat16* kb = Ks + (it & 1) * WM_KEYS * LDQ;
-            const __nv_bfloat16* vb = Vs + (it & 1) * WM_KEYS * LDV;
+            const __nv_bfloat16* kb = Ks + ((it % STAGES) * WM_KEYS + key0) * LDQ;
+            const __nv_bfloat16* vb = Vs + ((it % STAGES) * WM_KEYS + key0) * LDV;
             float s[8][4];
 #pragma unroll
             for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
             for (int ks = 0; ks < d.dk; ks += 16) {
                 uint32_t ah[4], al[4];
-                const int qoff = (warp * 16 + (lane & 15)) * LDQ + ks + (lane >> 4) * 8;
+                const int qoff = (row0 + (lane & 15)) * LDQ + ks + (lane >> 4) * 8;
                 ldsm_x4((uint32_t)__cvta_generic_to_shared(Qh + qoff), ah);
                 ldsm_x4((uint32_t)__cvta_generic_to_shared(Ql + qoff), al);
 #pragma unroll
                 for (int np = 0; np < 4; ++np) {
+                    if (np >= npw) break;
                     uint32_t b[4];
                     ldsm_x4((uint32_t)__cvta_generic_to_shared(kb + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LDQ + ks +
                                                                 ((lane >> 3) & 1) * 8), b);
@@ -331,9 +346,10 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             float txA = -INFINITY, txB = -INFINITY;
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
+                if (nt >= 2 * npw) break;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int kp = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const int kp = j0 + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int p = e < 2 ? pA : pB;
                     const bool seen = (e < 2 ? okA : okB) && kp < j_end && kp <= p && (p - kp < d.window || kp < d.keep_first);
                     const float v = seen ? s[nt][e] * d.scale : -INFINITY;
@@ -355,6 +371,7 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             float sumA = 0.f, sumB = 0.f;
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
+                if (nt >= 2 * npw) break;
                 s[nt][0] = expf(s[nt][0] - sA);
                 s[nt][1] = expf(s[nt][1] - sA);
                 s[nt][2] = expf(s[nt][2] - sB);
@@ -372,6 +389,7 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             // weights x values: 16 keys at a time, the weights as hi + lo bf16 terms
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
+                if (j >= npw) break;
                 uint32_t ph[4], pl[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
@@ -403,6 +421,39 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
     lA += __shfl_xor_sync(0xffffffffu, lA, 2);
     lB += __shfl_xor_sync(0xffffffffu, lB, 1);
     lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    if (ksplit) {
+        // every warp leaves its unnormalised share of rows 0 .. 15; the shares are merged per element, then the sink
+        if ((lane & 3) == 0) {
+            stage_ml[(warp * 16 + (lane >> 2)) * 2] = mA, stage_ml[(warp * 16 + (lane >> 2)) * 2 + 1] = lA;
+            stage_ml[(warp * 16 + (lane >> 2) + 8) * 2] = mB, stage_ml[(warp * 16 + (lane >> 2) + 8) * 2 + 1] = lB;
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (i < nvt) {
+                const int c = i * 8 + (lane & 3) * 2;
+                float* sa = stage + (warp * 16 + (lane >> 2)) * d.dv + c;
+                float* sb = sa + 8 * d.dv;
+                sa[0] = o[i][0], sa[1] = o[i][1];
+                sb[0] = o[i][2], sb[1] = o[i][3];
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < n_rows * d.dv; i += 128) {
+            const int r = i / d.dv, c = i % d.dv;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) mx = fmaxf(mx, stage_ml[(w * 16 + r) * 2]);
+            if (sink) mx = fmaxf(mx, sink[g * group + r % group]);
+            float num = 0.f, den = sink ? expf(sink[g * group + r % group] - mx) : 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = expf(stage_ml[(w * 16 + r) * 2] - mx);       // a share that saw no key: exp(-inf) = 0
+                den += stage_ml[(w * 16 + r) * 2 + 1] * f;
+                num += stage[(w * 16 + r) * d.dv + c] * f;
+            }
+            stage[r * d.dv + c] = num / den;       // only this thread reads column c of row r's shares
+        }
+    } else {
     float invA = 1.f / lA, invB = 1.f / lB;
     if (sink) {   // one more term of the denominator, without a value
         if (okA) {
@@ -421,6 +472,7 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             if (okA) stage[rA * d.dv + c] = o[i][0] * invA, stage[rA * d.dv + c + 1] = o[i][1] * invA;
             if (okB) stage[rB * d.dv + c] = o[i][2] * invB, stage[rB * d.dv + c + 1] = o[i][3] * invB;
         }
+    }
     }
     __syncthreads();
     for (int i = tid; i < n_rows * d.dv; i += 128) {
@@ -442,19 +494,32 @@ int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nse
                int of32, cudaStream_t stream) {
     const int group = d.heads / d.kv_heads;
     const int TQ = WM_ROWS / group;
-    const size_t smem = (size_t)(2 * WM_ROWS * (d.dk + 8) + 2 * WM_KEYS * (d.dk + 8) + 2 * WM_KEYS * (d.dv + 8)) * 2;
     dim3 grid((max_qlen + TQ - 1) / TQ, nseq, d.kv_heads);
+    // single-token steps are bound by the latency of the key/value stream: four tiles in flight when the grid leaves an
+    // SM to one CTA anyway, two (and two CTAs per SM) otherwise
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    const int stages = (max_qlen * group <= 16 && (long long)grid.x * grid.y * grid.z <= sms) ? 4 : 2;
+    const size_t smem = (size_t)(2 * WM_ROWS * (d.dk + 8) + stages * WM_KEYS * (d.dk + 8 + d.dv + 8)) * 2;
     if (grid.y > 65535 || grid.z > 65535) return set_error("windowed attention: too many sequences or heads");
-#define ASD_WM_CASE(N)                                                                                               \
+#define ASD_WM_LAUNCH(N, S)                                                                                          \
     {                                                                                                                \
-        auto fn = window_attn_mma<N>;                                                                                \
+        auto fn = window_attn_mma<N, S>;                                                                             \
         if (smem > 48 * 1024) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
         fn<<<grid, 128, smem, stream>>>(ix, cu_q, seq_slot, TQ, q, ldq, d, sink, freq_v, cache, out, of32);          \
+    }
+#define ASD_WM_CASE(N)            \
+    {                             \
+        if (stages == 4)          \
+            ASD_WM_LAUNCH(N, 4)   \
+        else                      \
+            ASD_WM_LAUNCH(N, 2)   \
     }
     if (d.dv <= 32) ASD_WM_CASE(4)
     else if (d.dv <= 64) ASD_WM_CASE(8)
     else ASD_WM_CASE(16)
 #undef ASD_WM_CASE
+#undef ASD_WM_LAUNCH
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
     return 0;
