@@ -221,11 +221,13 @@ struct WindowDims {
 int launch_window_post(const SeqIndex& ix, float* qkv, long long ld, const WindowDims& d, const float* freq_k,
                        const float* freq_v, const PagedRows& cache, cudaStream_t stream);
 // out[m][heads * dv] in the engine's element type: softmax (denominator + exp(sink[head])) over the visible positions,
-// turned back by the query's position.  sink fp32 [heads] (nullptr: none).  tiled = 0: one warp per (token, head).
+// turned back by the query's position.  sink fp32 [heads] (nullptr: none).  tiled = 0: one warp per (token, head);
+// else bf16 cache rows run on the tensor cores where the sizes allow.  ws (the AttnSplit workspace of the latent
+// kernels; o and ml may be nullptr) holds the partial results when single-token steps cut the keys into shares.
 int launch_window_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen,
                             int max_kv_len, const float* q, long long ldq, const WindowDims& d, const float* sink,
                             const float* freq_v, const PagedRows& cache, void* out, int of32, int tiled,
-                            cudaStream_t stream);
+                            const AttnSplit& ws, cudaStream_t stream);
 
 int preload_blocks();
 

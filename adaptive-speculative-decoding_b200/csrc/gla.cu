@@ -74,8 +74,9 @@ __global__ void __launch_bounds__(GD_CH) gla_decay_kernel(const float* a, long l
 
 // ROWS state rows per thread (a multiple of 4: the staged q, k and decay rows are read as float4); the staged rows are
 // padded with zeros up to warps x ROWS, so rows beyond dk keep a zero state and add nothing.
-template <int ROWS>
-__global__ void __launch_bounds__(256, 2) gla_recurrence_kernel(SeqIndex ix, const int* cu_q, const int* seq_slot,
+// CH positions are staged per chunk; MAXT bounds the CTA's threads (32 per slice of ROWS key rows).
+template <int ROWS, int MAXT, int CH>
+__global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 2 : 1) gla_recurrence_kernel(SeqIndex ix, const int* cu_q, const int* seq_slot,
                                                             const float* q, const float* k, const float* v, long long ld,
                                                             const float* alpha, GlaDims d, float* state, int ring,
                                                             float* out) {
@@ -91,7 +92,7 @@ __global__ void __launch_bounds__(256, 2) gla_recurrence_kernel(SeqIndex ix, con
     const int slot = seq_slot[seq];
     const int p0 = ix.positions[t0];
     // shared: two buffers of { q, k, decay [CH][dkp] each, v [CH][32] }, then the partial o [RS][CH][32]
-    const int buf_elems = 3 * GLA_CH * dkp + GLA_CH * 32;
+    const int buf_elems = 3 * CH * dkp + CH * 32;
     float* part = sm + 2 * buf_elems;
     const long long st_head = ((long long)head * d.dk) * d.dv;
     const long long st_entry = (long long)d.heads * d.dk * d.dv;
@@ -110,11 +111,11 @@ __global__ void __launch_bounds__(256, 2) gla_recurrence_kernel(SeqIndex ix, con
     // a chunk's rows arrive by 4-byte cp.async (any alignment), one chunk ahead of the arithmetic; rows beyond the
     // chunk's positions and key channels beyond dk are filled with zeros
     auto fetch = [&](int buf, int c0) {
-        const int nt = min(GLA_CH, t1 - c0);
+        const int nt = min(CH, t1 - c0);
         float* qd = sm + buf * buf_elems;
-        float* kd = qd + GLA_CH * dkp;
-        float* ad = kd + GLA_CH * dkp;
-        float* vd = ad + GLA_CH * dkp;
+        float* kd = qd + CH * dkp;
+        float* ad = kd + CH * dkp;
+        float* vd = ad + CH * dkp;
         for (int i = threadIdx.x; i < nt * dkp; i += nthr) {        // rows beyond the chunk's positions are never read
             const int t = i / dkp, c = i - t * dkp;
             const bool ok = c < d.dk;
@@ -132,19 +133,19 @@ __global__ void __launch_bounds__(256, 2) gla_recurrence_kernel(SeqIndex ix, con
     };
     fetch(0, t0);
     int it = 0;
-    for (int c0 = t0; c0 < t1; c0 += GLA_CH, ++it) {
-        const int nt = min(GLA_CH, t1 - c0);
-        if (c0 + GLA_CH < t1) {
-            fetch((it + 1) & 1, c0 + GLA_CH);
+    for (int c0 = t0; c0 < t1; c0 += CH, ++it) {
+        const int nt = min(CH, t1 - c0);
+        if (c0 + CH < t1) {
+            fetch((it + 1) & 1, c0 + CH);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();   // this chunk's rows have landed for every thread; the previous partial sums have been read
         const float* qs = sm + (it & 1) * buf_elems;
-        const float* ks = qs + GLA_CH * dkp;
-        const float* as = ks + GLA_CH * dkp;
-        const float* vs = as + GLA_CH * dkp;
+        const float* ks = qs + CH * dkp;
+        const float* as = ks + CH * dkp;
+        const float* vs = as + CH * dkp;
         for (int t = 0; t < nt; ++t) {
             const float vt = vs[t * 32 + lane];
             const float4* qt = reinterpret_cast<const float4*>(qs + t * dkp + r0);
@@ -163,7 +164,7 @@ __global__ void __launch_bounds__(256, 2) gla_recurrence_kernel(SeqIndex ix, con
                 o2 = fmaf(S[r + 2], q4.z, o2);
                 o3 = fmaf(S[r + 3], q4.w, o3);
             }
-            part[(warp * GLA_CH + t) * 32 + lane] = (o0 + o1) + (o2 + o3);
+            part[(warp * CH + t) * 32 + lane] = (o0 + o1) + (o2 + o3);
             // the last `ring` new positions leave their state behind
             const int m = c0 + t;
             if (t1 - m <= ring && col_ok) {
@@ -178,7 +179,7 @@ __global__ void __launch_bounds__(256, 2) gla_recurrence_kernel(SeqIndex ix, con
             const int t = i >> 5, c = i & 31;
             if (col0 + c >= d.dv) continue;
             float o = 0.f;
-            for (int w = 0; w < RS; ++w) o += part[(w * GLA_CH + t) * 32 + c];
+            for (int w = 0; w < RS; ++w) o += part[(w * CH + t) * 32 + c];
             out[(long long)(c0 + t) * d.heads * d.dv + hv + col0 + c] = o * d.q_scale;
         }
     }
@@ -211,8 +212,8 @@ int launch_gla_decay(const float* a, long long lda, const float* w_decay, const 
     if (d.low <= 0 || !(d.tau > 0.f)) return set_error("gla: decay projection of size %d, tau %f", d.low, d.tau);
     const size_t smem = (size_t)d.low * (GD_CH + GD_TOK) * sizeof(float);
     if (smem > 200 * 1024) return set_error("gla: decay projection of size %d does not fit shared memory", d.low);
-    if (smem > 48 * 1024)
-        ASD_CUDA(cudaFuncSetAttribute(gla_decay_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static PerDeviceOnce once;
+    if (once.need()) ASD_CUDA(cudaFuncSetAttribute(gla_decay_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     dim3 grid((d.heads * d.dk + GD_CH - 1) / GD_CH, (M + GD_TOK - 1) / GD_TOK);
     if (grid.y > 65535) return set_error("gla: too many tokens");
     gla_decay_kernel<<<grid, GD_CH, smem, stream>>>(a, lda, w_decay, b_decay, d, alpha, M);
@@ -225,26 +226,29 @@ int launch_gla_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_sl
                           const float* k, const float* v, long long ld, const float* alpha, const GlaDims& d,
                           float* state, int ring, float* out, cudaStream_t stream) {
     if (ix.M <= 0 || nseq <= 0) return 0;
-    if (d.dk <= 0 || d.dk > 8 * GLA_NR) return set_error("gla: key size %d outside 1..%d", d.dk, 8 * GLA_NR);
+    if (d.dk <= 0 || d.dk > 32 * GLA_NR) return set_error("gla: key size %d outside 1..%d", d.dk, 32 * GLA_NR);
     if (ring <= 0 || !state) return set_error("gla: no state");
     // the fewest state rows per thread (4, 8, 16 or 32) that at most eight warps cover
     int rows = 4;
-    while (rows * 8 < d.dk) rows *= 2;
-    const int RS = (d.dk + rows - 1) / rows;
+    while (rows < GLA_NR && rows * 8 < d.dk) rows *= 2;
+    const int RS = (d.dk + rows - 1) / rows;              // more than eight warps only for key sizes above 256
     const int dkp = RS * rows;
-    const size_t smem = (size_t)(2 * (3 * GLA_CH * dkp + GLA_CH * 32) + RS * GLA_CH * 32) * sizeof(float);
+    const int ch = RS <= 8 ? GLA_CH : GLA_CH / 4;         // shorter chunks keep the staged rows of a large head in shared memory
+    const size_t smem = (size_t)(2 * (3 * ch * dkp + ch * 32) + RS * ch * 32) * sizeof(float);
     dim3 grid(nseq, d.heads, (d.dv + 31) / 32);
     if (grid.y > 65535 || grid.z > 65535) return set_error("gla: too many heads or value columns");
-#define ASD_GLA_CASE(R)                                                                                               \
+#define ASD_GLA_CASE(R, T, C)                                                                                         \
     {                                                                                                                 \
-        auto fn = gla_recurrence_kernel<R>;                                                                           \
-        if (smem > 48 * 1024) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        auto fn = gla_recurrence_kernel<R, T, C>;                                                                        \
+        static PerDeviceOnce once;                                                                                    \
+        if (once.need()) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
         fn<<<grid, RS * 32, smem, stream>>>(ix, cu_q, seq_slot, q, k, v, ld, alpha, d, state, ring, out);             \
     }
-    if (rows == 4) ASD_GLA_CASE(4)
-    else if (rows == 8) ASD_GLA_CASE(8)
-    else if (rows == 16) ASD_GLA_CASE(16)
-    else ASD_GLA_CASE(32)
+    if (RS > 8) ASD_GLA_CASE(32, 1024, GLA_CH / 4)
+    else if (rows == 4) ASD_GLA_CASE(4, 256, GLA_CH)
+    else if (rows == 8) ASD_GLA_CASE(8, 256, GLA_CH)
+    else if (rows == 16) ASD_GLA_CASE(16, 256, GLA_CH)
+    else ASD_GLA_CASE(32, 256, GLA_CH)
 #undef ASD_GLA_CASE
     count_launch(1);
     ASD_CUDA(cudaGetLastError());

@@ -120,8 +120,8 @@ int launch_row_close(const RowClose& c, cudaStream_t stream) {
     if (c.D <= 0 || ((c.next_w || c.cat) && !c.hn)) return set_error("row_close: bad arguments");
     const size_t smem = (size_t)(c.D + 33) * sizeof(float);
     if (smem > 200 * 1024) return set_error("row_close: width %d does not fit shared memory", c.D);
-    if (smem > 48 * 1024)
-        ASD_CUDA(cudaFuncSetAttribute(row_close_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static PerDeviceOnce once;
+    if (once.need()) ASD_CUDA(cudaFuncSetAttribute(row_close_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     row_close_kernel<<<c.M, row_threads(c.D), smem, stream>>>(c);
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
@@ -141,8 +141,8 @@ int launch_polynorm(const float* z, const float* coeff, float eps, void* out, in
     if (M <= 0 || F <= 0) return 0;
     const int staged = (size_t)F * sizeof(float) <= 96 * 1024;
     const size_t smem = (33 + (staged ? (size_t)F : 0)) * sizeof(float);
-    if (smem > 48 * 1024)
-        ASD_CUDA(cudaFuncSetAttribute(polynorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static PerDeviceOnce once;
+    if (once.need()) ASD_CUDA(cudaFuncSetAttribute(polynorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     polynorm_kernel<<<M, row_threads(F), smem, stream>>>(z, coeff, eps, out, of32, F, staged);
     count_launch(1);
     ASD_CUDA(cudaGetLastError());

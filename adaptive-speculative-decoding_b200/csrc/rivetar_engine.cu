@@ -204,7 +204,7 @@ static int mix_window(RvEngine* e, const RvLayer& ly, const RvRun& run, int li, 
     }
     RV_PROF(RV_WINDOW_ATTN);
     return launch_window_attention(b.ix, b.cu_q, b.seq_slot, b.nseq, b.max_qlen, b.max_kv_len, e->proj, ly.n_in, wd,
-                                   ly.f("sink"), ly.freq_v, cache, e->mixed, f32, e->fused_attn, s);
+                                   ly.f("sink"), ly.freq_v, cache, e->mixed, f32, e->fused_attn, e->attn_ws, s);
 }
 
 static int forward(RvEngine* e, const Batch& b, const int* logit_rows, int n_rows, float* logits, long long ld,

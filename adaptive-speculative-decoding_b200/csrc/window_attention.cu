@@ -22,6 +22,8 @@ namespace asd {
 
 namespace {
 
+__device__ __forceinline__ int warp_of(unsigned tid) { return (int)(tid >> 5); }
+
 __device__ __forceinline__ long long wcache_row(const PagedRows& c, int slot, int pos) {
     const int page = c.page_table[(long long)slot * c.max_pages + pos / c.page_size];
     return (long long)page * c.page_size + pos % c.page_size;
@@ -69,8 +71,9 @@ __global__ void window_post_kernel(SeqIndex ix, float* qkv, long long ld, Window
 
 template <typename T, int ACC>   // ACC = ceil(dv / 32) accumulators per lane
 __global__ void __launch_bounds__(512) window_attn_kernel(SeqIndex ix, const int* cu_q, const int* seq_slot, int TQ,
-                                                           const float* q, long long ldq, WindowDims d, const float* sink,
-                                                           const float* freq_v, PagedRows cache, void* out, int of32) {
+                                                           int hpc, const float* q, long long ldq, WindowDims d,
+                                                           const float* sink, const float* freq_v, PagedRows cache, void* out,
+                                                           int of32) {
     extern __shared__ float smem[];
     const int group = d.heads / d.kv_heads;
     const int LDK = d.dk | 1;                          // odd row stride: lanes reading one column hit 32 banks
@@ -79,14 +82,16 @@ __global__ void __launch_bounds__(512) window_attn_kernel(SeqIndex ix, const int
     float* vs = ks + 32 * LDK;                         // [32][dv]
     float* qs = vs + 32 * d.dv;                        // [warps][dk]
     float* os = qs + nwarps * d.dk;                    // [warps][dv]
-    const int seq = blockIdx.y, g = blockIdx.z;
+    // a CTA takes hpc query heads of one key/value head (all of them unless there are more than 16)
+    const int nsub = (group + hpc - 1) / hpc;
+    const int seq = blockIdx.y, g = blockIdx.z / nsub, h_in_group = (blockIdx.z % nsub) * hpc + warp_of(threadIdx.x) % hpc;
     const int t0 = cu_q[seq] + blockIdx.x * TQ, t_end = cu_q[seq + 1];
     if (t0 >= t_end) return;
     const int slot = seq_slot[seq];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tq = warp / group, head = g * group + warp % group;
+    const int tq = warp / hpc, head = g * group + h_in_group;
     const int m = t0 + tq;
-    const bool live = m < t_end;
+    const bool live = m < t_end && h_in_group < group;
     const int p = live ? ix.positions[m] : -1;
     const int n_tok = min(TQ, t_end - t0);
     const int p_first = ix.positions[t0], p_last = p_first + n_tok - 1;
@@ -183,21 +188,22 @@ int launch_simple(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int 
                   long long ldq, const WindowDims& d, const float* sink, const float* freq_v, const PagedRows& cache,
                   void* out, int of32, cudaStream_t stream) {
     const int group = d.heads / d.kv_heads;
-    if (group > 16) return set_error("windowed attention: %d query heads per key/value head (at most 16)", group);
-    int TQ = 16 / group;
-    if (TQ < 1) TQ = 1;
+    const int hpc = group < 16 ? group : 16;     // query heads per CTA
+    const int nsub = (group + hpc - 1) / hpc;
+    int TQ = 16 / hpc;
     while (TQ > 1 && TQ / 2 >= max_qlen) TQ /= 2;
-    const int warps = TQ * group;
+    const int warps = TQ * hpc;
     const size_t smem = (size_t)(32 * (d.dk | 1) + 32 * d.dv + warps * (d.dk + d.dv)) * sizeof(float);
     if (smem > 220 * 1024) return set_error("windowed attention: head sizes %d / %d do not fit shared memory", d.dk, d.dv);
-    dim3 grid((max_qlen + TQ - 1) / TQ, nseq, d.kv_heads);
+    dim3 grid((max_qlen + TQ - 1) / TQ, nseq, d.kv_heads * nsub);
     if (grid.y > 65535 || grid.z > 65535) return set_error("windowed attention: too many sequences or heads");
     const int acc = (d.dv + 31) / 32;
 #define ASD_WIN_CASE(A)                                                                                              \
     {                                                                                                                \
         auto fn = window_attn_kernel<T, A>;                                                                          \
-        if (smem > 48 * 1024) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        fn<<<grid, warps * 32, smem, stream>>>(ix, cu_q, seq_slot, TQ, q, ldq, d, sink, freq_v, cache, out, of32);   \
+        static PerDeviceOnce once;                                                                                   \
+        if (once.need()) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
+        fn<<<grid, warps * 32, smem, stream>>>(ix, cu_q, seq_slot, TQ, hpc, q, ldq, d, sink, freq_v, cache, out, of32); \
     }
     if (acc <= 1) ASD_WIN_CASE(1)
     else if (acc <= 2) ASD_WIN_CASE(2)
@@ -214,6 +220,7 @@ int launch_simple(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int 
 // ---------------------------------------------------------------------------------------------------------------
 // Tensor-core form.  Row r of the CTA's 64 is (token r / group, query head r % group of key/value head g).
 constexpr int WM_ROWS = 64, WM_KEYS = 64;
+constexpr int kMaxSmem = 220 * 1024;   // dynamic shared memory a CTA may ask for (the opt-in limit less the static part)
 
 __device__ __forceinline__ void split2(float x, __nv_bfloat16& hi, __nv_bfloat16& lo) {
     hi = __float2bfloat16(x);
@@ -222,21 +229,24 @@ __device__ __forceinline__ void split2(float x, __nv_bfloat16& hi, __nv_bfloat16
 
 // STAGES key/value tiles are in flight.  When the CTA has at most 16 rows (single-token steps), all four warps take
 // those rows and a quarter of every tile's keys each, and their partial results are merged at the end.
-template <int NV, int STAGES>   // value column tiles of 8: dv <= 8 * NV
+// SINGLE: every CTA of the launch is of that kind (single-token steps); the query fragments then stay in registers.
+template <int NV, int STAGES, bool SINGLE>   // value column tiles of 8: dv <= 8 * NV
 __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* cu_q, const int* seq_slot, int TQ,
                                                        const float* q, long long ldq, WindowDims d, const float* sink,
-                                                       const float* freq_v, PagedRows cache, void* out, int of32) {
+                                                       const float* freq_v, PagedRows cache, void* out, int of32,
+                                                       int nsplit, float* ws_o, float* ws_ml, int q_alloc) {
     extern __shared__ __align__(16) unsigned char smraw[];
     const int LDQ = d.dk + 8, LDV = d.dv + 8;   // bf16 elements; 16 bytes of padding keep ldmatrix rows on distinct banks
-    __nv_bfloat16* Qh = reinterpret_cast<__nv_bfloat16*>(smraw);   // [64][LDQ]
-    __nv_bfloat16* Ql = Qh + WM_ROWS * LDQ;
-    __nv_bfloat16* Ks = Ql + WM_ROWS * LDQ;                        // [STAGES][64][LDQ]
+    __nv_bfloat16* Qh = reinterpret_cast<__nv_bfloat16*>(smraw);   // [q_alloc][LDQ]: 64 rows, or 16 for single-token steps
+    __nv_bfloat16* Ql = Qh + q_alloc * LDQ;
+    __nv_bfloat16* Ks = Ql + q_alloc * LDQ;                        // [STAGES][64][LDQ]
     __nv_bfloat16* Vs = Ks + STAGES * WM_KEYS * LDQ;               // [STAGES][64][LDV]
     float* stage = reinterpret_cast<float*>(Ks);                   // [64][dv] once the last tile is consumed
     float* stage_ml = stage + WM_ROWS * d.dv;                      // [64][2]: maximum and sum of every warp's share
     const int group = d.heads / d.kv_heads;
     const int seq = blockIdx.y, g = blockIdx.z;
-    const int t0 = cu_q[seq] + blockIdx.x * TQ, t_end = cu_q[seq + 1];
+    const int split = blockIdx.x % nsplit;       // this CTA's share of the key tiles (single-token steps only)
+    const int t0 = cu_q[seq] + (blockIdx.x / nsplit) * TQ, t_end = cu_q[seq + 1];
     if (t0 >= t_end) return;
     const int slot = seq_slot[seq];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -246,7 +256,9 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
     if (lo < 0) lo = 0;
     const int first_end = d.keep_first < lo ? d.keep_first : lo;
     const int nA = (first_end + WM_KEYS - 1) / WM_KEYS, nB = (p_last + 1 - lo + WM_KEYS - 1) / WM_KEYS;
-    const int ntiles = nA + nB;
+    const int all_tiles = nA + nB, per_split = (all_tiles + nsplit - 1) / nsplit;
+    const int tile0 = split * per_split;
+    const int ntiles = max(0, min(all_tiles, tile0 + per_split) - tile0);      // tiles tile0 .. tile0 + ntiles - 1 are this CTA's
     // queries as hi + lo bf16 terms
     const int q_rows = n_rows <= 16 ? 16 : WM_ROWS;      // rows the products read (the rest of a single-token tile is unused)
     for (int r = warp; r < q_rows; r += 4) {
@@ -262,6 +274,7 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
     const int nk = d.kv_heads * d.dk, rowlen = nk + d.kv_heads * d.dv;
     const int ck = d.dk >> 3, cpr = (d.dk + d.dv) >> 3;
     auto tile_range = [&](int i, int& j0, int& j_end) {
+        i += tile0;
         if (i < nA) {
             j0 = i * WM_KEYS;
             j_end = first_end;
@@ -271,7 +284,8 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
         }
     };
     // two threads per key row: one page lookup each (made a tile ahead of the copies that need it), then every other
-    // 16-byte chunk of the row's keys and values
+    // 16-byte chunk of the row's keys and values.  (Consecutive lanes on consecutive chunks of a row, with the row
+    // offsets handed over through shared memory, measured slower: 99 against 78 us at 64 sequences.)
     auto lookup = [&](int i) -> long long {
         if (i >= ntiles) return 0;
         int j0, j_end;
@@ -294,7 +308,8 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
         for (int cc = tid & 1; cc < cpr - ck; cc += 2)
             cp_async16((uint32_t)__cvta_generic_to_shared(vd + r * LDV + cc * 8), vsrc + cc * 8, ok);
     };
-    const bool ksplit = n_rows <= 16;                     // every warp: rows 0 .. 15, keys [16 warp, 16 warp + 16) of a tile
+    constexpr int NP = SINGLE ? 1 : 4;                    // pairs of 8-key score tiles per warp and tile at most
+    const bool ksplit = SINGLE || n_rows <= 16;           // every warp: rows 0 .. 15, keys [16 warp, 16 warp + 16) of a tile
     const int row0 = ksplit ? 0 : warp * 16, key0 = ksplit ? warp * 16 : 0, npw = ksplit ? 1 : 4;
     const int rA = row0 + (lane >> 2), rB = rA + 8;
     const bool okA = rA < n_rows, okB = rB < n_rows;
@@ -311,6 +326,20 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
         cp_async_commit();
     }
     long long next_off = lookup(STAGES - 1);
+    // single-token steps: the 16 query rows are the same for every tile and warp, their fragments are loaded once
+    uint32_t qh[SINGLE ? 8 : 1][4], ql[SINGLE ? 8 : 1][4];
+    const bool q_regs = SINGLE && d.dk <= 128;
+    if (q_regs) {
+        __syncthreads();   // the queries are in place
+#pragma unroll
+        for (int k8 = 0; k8 < (SINGLE ? 8 : 1); ++k8) {
+            if (k8 * 16 < d.dk) {
+                const int qoff = (lane & 15) * LDQ + k8 * 16 + (lane >> 4) * 8;
+                ldsm_x4((uint32_t)__cvta_generic_to_shared(Qh + qoff), qh[k8]);
+                ldsm_x4((uint32_t)__cvta_generic_to_shared(Ql + qoff), ql[k8]);
+            }
+        }
+    }
     for (int it = 0; it < ntiles; ++it) {
         if (it + STAGES - 1 < ntiles) load_tile((it + STAGES - 1) % STAGES, it + STAGES - 1, next_off);
         cp_async_commit();                 // (an empty group keeps the count of groups in flight uniform)
@@ -322,16 +351,30 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             tile_range(it, j0, j_end);
             const __nv_bfloat16* kb = Ks + ((it % STAGES) * WM_KEYS + key0) * LDQ;
             const __nv_bfloat16* vb = Vs + ((it % STAGES) * WM_KEYS + key0) * LDV;
-            float s[8][4];
+            float s[2 * NP][4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+            for (int i = 0; i < 2 * NP; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+            if (q_regs) {
+#pragma unroll
+                for (int k8 = 0; k8 < (SINGLE ? 8 : 1); ++k8) {
+                    if (k8 * 16 < d.dk) {
+                        uint32_t b[4];
+                        ldsm_x4((uint32_t)__cvta_generic_to_shared(kb + ((lane & 7) + ((lane >> 4) & 1) * 8) * LDQ + k8 * 16 +
+                                                                    ((lane >> 3) & 1) * 8), b);
+                        mma_bf16(s[0], qh[k8], b[0], b[1]);
+                        mma_bf16(s[0], ql[k8], b[0], b[1]);
+                        mma_bf16(s[1], qh[k8], b[2], b[3]);
+                        mma_bf16(s[1], ql[k8], b[2], b[3]);
+                    }
+                }
+            } else
             for (int ks = 0; ks < d.dk; ks += 16) {
                 uint32_t ah[4], al[4];
                 const int qoff = (row0 + (lane & 15)) * LDQ + ks + (lane >> 4) * 8;
                 ldsm_x4((uint32_t)__cvta_generic_to_shared(Qh + qoff), ah);
                 ldsm_x4((uint32_t)__cvta_generic_to_shared(Ql + qoff), al);
 #pragma unroll
-                for (int np = 0; np < 4; ++np) {
+                for (int np = 0; np < NP; ++np) {
                     if (np >= npw) break;
                     uint32_t b[4];
                     ldsm_x4((uint32_t)__cvta_generic_to_shared(kb + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LDQ + ks +
@@ -345,7 +388,7 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             // mask, running maxima
             float txA = -INFINITY, txB = -INFINITY;
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
+            for (int nt = 0; nt < 2 * NP; ++nt) {
                 if (nt >= 2 * npw) break;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -366,29 +409,31 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             txB = fmaxf(txB, __shfl_xor_sync(0xffffffffu, txB, 2));
             const float nA_ = fmaxf(mA, txA), nB_ = fmaxf(mB, txB);
             const float sA = nA_ == -INFINITY ? 0.f : nA_, sB = nB_ == -INFINITY ? 0.f : nB_;   // nothing seen yet: weights 0
-            const float cA = expf(mA - sA), cB = expf(mB - sB);
+            const float cA = __expf(mA - sA), cB = __expf(mB - sB);
             mA = nA_, mB = nB_;
             float sumA = 0.f, sumB = 0.f;
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
+            for (int nt = 0; nt < 2 * NP; ++nt) {
                 if (nt >= 2 * npw) break;
-                s[nt][0] = expf(s[nt][0] - sA);
-                s[nt][1] = expf(s[nt][1] - sA);
-                s[nt][2] = expf(s[nt][2] - sB);
-                s[nt][3] = expf(s[nt][3] - sB);
+                s[nt][0] = __expf(s[nt][0] - sA);
+                s[nt][1] = __expf(s[nt][1] - sA);
+                s[nt][2] = __expf(s[nt][2] - sB);
+                s[nt][3] = __expf(s[nt][3] - sB);
                 sumA += s[nt][0] + s[nt][1];
                 sumB += s[nt][2] + s[nt][3];
             }
             lA = lA * cA + sumA;
             lB = lB * cB + sumB;
+            if (__any_sync(0xffffffffu, cA != 1.f || cB != 1.f)) {      // no row of the warp met a new maximum: nothing to rescale
 #pragma unroll
-            for (int i = 0; i < NV; ++i) {
-                o[i][0] *= cA, o[i][1] *= cA;
-                o[i][2] *= cB, o[i][3] *= cB;
+                for (int i = 0; i < NV; ++i) {
+                    o[i][0] *= cA, o[i][1] *= cA;
+                    o[i][2] *= cB, o[i][3] *= cB;
+                }
             }
             // weights x values: 16 keys at a time, the weights as hi + lo bf16 terms
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < NP; ++j) {
                 if (j >= npw) break;
                 uint32_t ph[4], pl[4];
 #pragma unroll
@@ -438,6 +483,26 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             }
         }
         __syncthreads();
+        if (nsplit > 1) {
+            // this CTA saw a share of the keys: its merged maximum, sum and unnormalised result wait for the combine kernel
+            for (int i = tid; i < n_rows * d.dv; i += 128) {
+                const int r = i / d.dv, c = i % d.dv;
+                float mx = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) mx = fmaxf(mx, stage_ml[(w * 16 + r) * 2]);
+                float num = 0.f, den = 0.f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const float f = mx == -INFINITY ? 0.f : expf(stage_ml[(w * 16 + r) * 2] - mx);
+                    den += stage_ml[(w * 16 + r) * 2 + 1] * f;
+                    num += stage[(w * 16 + r) * d.dv + c] * f;
+                }
+                const long long pair = ((long long)(t0 + r / group) * d.heads + g * group + r % group) * nsplit + split;
+                ws_o[pair * d.dv + c] = num;
+                if (c == 0) ws_ml[pair * 2] = mx, ws_ml[pair * 2 + 1] = den;
+            }
+            return;
+        }
         for (int i = tid; i < n_rows * d.dv; i += 128) {
             const int r = i / d.dv, c = i % d.dv;
             float mx = -INFINITY;
@@ -483,37 +548,82 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
     }
 }
 
+// merges the shares of a (token, head) pair's keys: one CTA per pair, one thread per value column; then the sink, the
+// normalisation and the turn back by the token's position
+__global__ void window_combine_kernel(SeqIndex ix, WindowDims d, const float* sink, const float* freq_v, int nsplit,
+                                      const float* ws_o, const float* ws_ml, void* out, int of32) {
+    extern __shared__ float row[];   // [dv]
+    const long long pair = blockIdx.x;
+    const int m = (int)(pair / d.heads), head = (int)(pair % d.heads);
+    float mx = sink ? sink[head] : -INFINITY;
+    for (int sp = 0; sp < nsplit; ++sp) mx = fmaxf(mx, ws_ml[(pair * nsplit + sp) * 2]);
+    float den = sink ? expf(sink[head] - mx) : 0.f;
+    for (int sp = 0; sp < nsplit; ++sp) den += ws_ml[(pair * nsplit + sp) * 2 + 1] * expf(ws_ml[(pair * nsplit + sp) * 2] - mx);
+    for (int c = threadIdx.x; c < d.dv; c += blockDim.x) {
+        float num = 0.f;
+        for (int sp = 0; sp < nsplit; ++sp)
+            num += ws_o[(pair * nsplit + sp) * d.dv + c] * expf(ws_ml[(pair * nsplit + sp) * 2] - mx);
+        row[c] = num / den;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < d.dv; c += blockDim.x)
+        stx(out, pair * d.dv + c, of32, turned(row, c, d.dv, d.interleaved, (float)ix.positions[m], freq_v, -1.f));
+}
+
 bool mma_supports(const WindowDims& d, const PagedRows& cache) {
     const int group = d.heads / d.kv_heads;
     return !cache.f32 && (d.dk % 16) == 0 && (d.dv % 16) == 0 && d.dv <= 128 && d.dk <= 256 && group <= WM_ROWS &&
            (reinterpret_cast<uintptr_t>(cache.pool) & 15) == 0;
 }
 
-int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, const float* q,
-               long long ldq, const WindowDims& d, const float* sink, const float* freq_v, const PagedRows& cache, void* out,
-               int of32, cudaStream_t stream) {
+int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, int max_kv_len,
+               const float* q, long long ldq, const WindowDims& d, const float* sink, const float* freq_v,
+               const PagedRows& cache, void* out, int of32, const AttnSplit& ws, cudaStream_t stream) {
     const int group = d.heads / d.kv_heads;
     const int TQ = WM_ROWS / group;
     dim3 grid((max_qlen + TQ - 1) / TQ, nseq, d.kv_heads);
+    // Single-token steps with few sequences leave most SMs without a CTA and every CTA with one long chain of tiles: the
+    // key tiles are then cut into shares for several CTAs, whose partial results the combine kernel merges.
+    static const int sms = []() {
+        int n = 148, dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        return n;
+    }();
+    int nsplit = 1;
+    if (max_qlen * group <= 16 && ws.o && ws.ml) {
+        const long long ctas = (long long)nseq * d.kv_heads;
+        const long long keys = (long long)(d.window < max_kv_len ? d.window : max_kv_len) + d.keep_first;
+        const int tiles = (int)((keys + WM_KEYS - 1) / WM_KEYS) + 1;
+        while (nsplit < 8 && ctas * nsplit < 2LL * sms && tiles >= 4 * nsplit) nsplit *= 2;
+        while (nsplit > 1 && ((long long)ix.M * d.heads * nsplit > ws.rows || (long long)ix.M * d.heads * nsplit * d.dv > ws.o_elems))
+            nsplit /= 2;
+    }
+    grid.x *= nsplit;
     // single-token steps are bound by the latency of the key/value stream: four tiles in flight when the grid leaves an
     // SM to one CTA anyway, two (and two CTAs per SM) otherwise
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
-    const int stages = (max_qlen * group <= 16 && (long long)grid.x * grid.y * grid.z <= sms) ? 4 : 2;
-    const size_t smem = (size_t)(2 * WM_ROWS * (d.dk + 8) + stages * WM_KEYS * (d.dk + 8 + d.dv + 8)) * 2;
+    const bool single = max_qlen * group <= 16;          // every CTA has at most 16 rows: a small query buffer, more tiles in flight
+    const int stages = !single ? 2 : ((long long)grid.x * grid.y * grid.z <= sms ? 4 : 3);
+    const int q_alloc = single ? 16 : WM_ROWS;
+    const size_t smem = (size_t)(2 * q_alloc * (d.dk + 8) + stages * WM_KEYS * (d.dk + 8 + d.dv + 8)) * 2;
+    if (smem > (size_t)kMaxSmem) return set_error("windowed attention: head sizes %d / %d do not fit shared memory", d.dk, d.dv);
     if (grid.y > 65535 || grid.z > 65535) return set_error("windowed attention: too many sequences or heads");
-#define ASD_WM_LAUNCH(N, S)                                                                                          \
+#define ASD_WM_LAUNCH(N, S, G)                                                                                       \
     {                                                                                                                \
-        auto fn = window_attn_mma<N, S>;                                                                             \
-        if (smem > 48 * 1024) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        fn<<<grid, 128, smem, stream>>>(ix, cu_q, seq_slot, TQ, q, ldq, d, sink, freq_v, cache, out, of32);          \
+        auto fn = window_attn_mma<N, S, G>;                                                                           \
+        static PerDeviceOnce once;   /* the attribute is set once per device: a host call per launch costs microseconds */ \
+        if (once.need()) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem)); \
+        fn<<<grid, 128, smem, stream>>>(ix, cu_q, seq_slot, TQ, q, ldq, d, sink, freq_v, cache, out, of32, nsplit,   \
+                                        ws.o, ws.ml, q_alloc);                                                       \
     }
 #define ASD_WM_CASE(N)            \
     {                             \
-        if (stages == 4)          \
-            ASD_WM_LAUNCH(N, 4)   \
-        else                      \
-            ASD_WM_LAUNCH(N, 2)   \
+        if (stages == 4)                \
+            ASD_WM_LAUNCH(N, 4, true)   \
+        else if (stages == 3)           \
+            ASD_WM_LAUNCH(N, 3, true)   \
+        else                            \
+            ASD_WM_LAUNCH(N, 2, false)  \
     }
     if (d.dv <= 32) ASD_WM_CASE(4)
     else if (d.dv <= 64) ASD_WM_CASE(8)
@@ -522,6 +632,12 @@ int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nse
 #undef ASD_WM_LAUNCH
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
+    if (nsplit > 1) {
+        window_combine_kernel<<<ix.M * d.heads, d.dv < 128 ? 64 : 128, d.dv * sizeof(float), stream>>>(
+            ix, d, sink, freq_v, nsplit, ws.o, ws.ml, out, of32);
+        count_launch(1);
+        ASD_CUDA(cudaGetLastError());
+    }
     return 0;
 }
 
@@ -541,8 +657,8 @@ int launch_window_post(const SeqIndex& ix, float* qkv, long long ld, const Windo
     if (check_dims(d)) return -1;
     const size_t smem = (size_t)(d.heads * d.dk + d.kv_heads * (d.dk + d.dv)) * sizeof(float);
     if (smem > 200 * 1024) return set_error("windowed attention: a token's q | k | v row does not fit shared memory");
-    if (smem > 48 * 1024)
-        ASD_CUDA(cudaFuncSetAttribute(window_post_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static PerDeviceOnce once;
+    if (once.need()) ASD_CUDA(cudaFuncSetAttribute(window_post_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     window_post_kernel<<<ix.M, 256, smem, stream>>>(ix, qkv, ld, d, freq_k, freq_v, cache);
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
@@ -552,12 +668,11 @@ int launch_window_post(const SeqIndex& ix, float* qkv, long long ld, const Windo
 int launch_window_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen,
                             int max_kv_len, const float* q, long long ldq, const WindowDims& d, const float* sink,
                             const float* freq_v, const PagedRows& cache, void* out, int of32, int tiled,
-                            cudaStream_t stream) {
+                            const AttnSplit& ws, cudaStream_t stream) {
     if (ix.M <= 0 || nseq <= 0) return 0;
     if (check_dims(d)) return -1;
-    (void)max_kv_len;
     if (tiled && mma_supports(d, cache))
-        return launch_mma(ix, cu_q, seq_slot, nseq, max_qlen, q, ldq, d, sink, freq_v, cache, out, of32, stream);
+        return launch_mma(ix, cu_q, seq_slot, nseq, max_qlen, max_kv_len, q, ldq, d, sink, freq_v, cache, out, of32, ws, stream);
     return cache.f32 ? launch_simple<float>(ix, cu_q, seq_slot, nseq, max_qlen, q, ldq, d, sink, freq_v, cache, out, of32, stream)
                      : launch_simple<__nv_bfloat16>(ix, cu_q, seq_slot, nseq, max_qlen, q, ldq, d, sink, freq_v, cache, out, of32, stream);
 }

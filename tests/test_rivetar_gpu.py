@@ -164,13 +164,30 @@ def test_polynomial_activation_alone():
 
 
 @pytest.mark.parametrize("entry", [gla(heads=3, dim=20, vdim=12, tau=2.0), gla(heads=1, dim=64, vdim=40, tau=30.0),
-                                   gla(heads=2, dim=130, vdim=33, tau=16.0, decay_rank=1)], ids=["a", "b", "c"])
+                                   gla(heads=2, dim=130, vdim=33, tau=16.0, decay_rank=1),
+                                   gla(heads=1, dim=300, vdim=20, tau=50.0, decay_rank=2)], ids=["a", "b", "c", "wide"])
 def test_gated_linear_attention_alone(entry):
     cfg = config([entry])
     w = O.random_model(cfg, seed=7)
     ids = tokens(70, 96, 8)
     ref, _ = O.forward(cfg, w, ids)
     assert rel_err(run_whole(cfg, w, ids, max_tokens=128), ref)[1] < 2e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_many_query_heads_per_key_value_head(dtype):
+    """twenty query heads share each key/value head: more than one CTA's worth in the one-warp-per-pair kernel, a row
+    tile that the group does not divide in the tensor-core kernel"""
+    cfg = config([window(heads=40, kv_heads=2, dim=16, vdim=16, size=30, keep_first=2, rot_dims=16, ff=0)])
+    w = O.random_model(cfg, seed=45)
+    ids = tokens(80, 96, 46)
+    ref, _ = O.forward(cfg, w, ids)
+    for cuts in ([80], [60] + [1] * 20, [7] * 12):
+        eng = make_engine(cfg, w, dtype=dtype, max_tokens=128)
+        slot = eng.open_sequence()
+        got = feed(eng, slot, ids, cuts)
+        assert (rel_err(got, ref)[1] < 2e-4) if dtype == torch.float32 else (rel_err(got, ref)[0] < 5e-2)
+        close(eng)
 
 
 def test_latent_attention_alone_both_pairings():
@@ -390,6 +407,25 @@ def test_both_windowed_attention_kernels_agree():
                 close(eng)
                 assert rel_err(got[-1], ref)[0] < 5e-2, (heads, kv_heads, cuts, fused)
             assert rel_err(got[0], got[1].cpu())[0] < 2e-3, (heads, kv_heads, cuts)
+
+
+def test_single_token_steps_with_key_shares_over_several_ctas():
+    """a long window and one sequence: single-token steps cut the key tiles into shares for several CTAs and merge them,
+    with the sink entering once, after the merge"""
+    cfg = config([window(heads=4, kv_heads=2, dim=32, vdim=32, size=800, keep_first=5, rot_dims=16, scale=0.3, ff=0)])
+    w = O.random_model(cfg, seed=43)
+    w["l0.mix.sink"] = torch.tensor([4.0, -1.0, 0.0, 2.0])
+    ids = tokens(900, 96, 44)
+    ref, _ = O.forward(cfg, w, ids)
+    got = []
+    for fused in (1, 0):
+        eng = make_engine(cfg, w, dtype=torch.bfloat16, max_tokens=1024, max_seq_len=1024)
+        eng.set_option("fused_attn", fused)
+        slot = eng.open_sequence()
+        got.append(feed(eng, slot, ids, [870] + [1] * 30)[870:])
+        close(eng)
+        assert rel_err(got[-1], ref[870:])[0] < 5e-2
+    assert rel_err(got[0], got[1].cpu())[0] < 2e-3
 
 
 # ------------------------------------------------------------------------------------------------ bf16 engine
