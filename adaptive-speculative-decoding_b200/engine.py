@@ -587,7 +587,7 @@ class RivetarEngine(_SlotOps, _BatchOps):
     verification does after a rejected tail - continues from the right state; a forward that starts a slot at
     position 0 starts from zero, so reused slots carry nothing over.
     ``dtype``: torch.bfloat16 (bf16 matrices / caches / matrix inputs, fp32 accumulation) or torch.float32 (true fp32
-    everywhere).  Same ``forward`` contract as ``QwenEngine``, so ``SpecDecoder`` and ``Stage`` drive it unchanged."""
+    everywhere).  Same ``forward`` interface as ``QwenEngine``, so ``SpecDecoder`` and ``Stage`` drive it unchanged."""
 
     TYPE_CODE = {"latent_attention": 0, "gla": 1, "attention": 2}
 

@@ -377,7 +377,7 @@ ASD_API int asd_rivetar_set_cache(asd_rivetar_engine_t* e, void* pool, int num_p
 /* options: "tc_linear", "tc_min_rows", "attn_tiled" as for the Mezilix engine; "fused_attn" (1, default: tiled windowed
  * attention kernel; 0: one warp per (token, head)); "profile" */
 ASD_API int asd_rivetar_set_option(asd_rivetar_engine_t* e, const char* name, int value);
-/* Same contract as asd_engine_forward (M <= max_tokens).  layer_out (optional, fp32 [runs][M][width]) receives the
+/* Same arguments as asd_engine_forward (M <= max_tokens).  layer_out (optional, fp32 [runs][M][width]) receives the
  * stream that leaves every layer execution. */
 ASD_API int asd_rivetar_forward(asd_rivetar_engine_t* e, const int32_t* tokens, const int32_t* positions,
                                 const int32_t* token_slot, int M, const int32_t* cu_q, const int32_t* seq_slot, int nseq,
