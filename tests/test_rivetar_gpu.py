@@ -428,6 +428,58 @@ def test_single_token_steps_with_key_shares_over_several_ctas():
     assert rel_err(got[0], got[1].cpu())[0] < 2e-3
 
 
+def random_config(seed):
+    """layers in any order and number with sizes drawn at random (multiples of 16 and of nothing), a span anywhere"""
+    g = torch.Generator().manual_seed(seed)
+    pick = lambda xs: xs[int(torch.randint(0, len(xs), (1,), generator=g))]
+    n = pick([2, 3, 4, 5])
+    layers = []
+    for _ in range(n):
+        kind = pick(["latent", "gla", "window"])
+        ff = pick([0, 24, 64, 100])
+        if kind == "latent":
+            rot_dim = pick([4, 8, 16, 32])
+            layers.append(latent(heads=pick([1, 2, 4, 5]), dim=pick([8, 16, 24, 64]), rot_dim=rot_dim, vdim=pick([8, 16, 20, 48]),
+                                 kv_rank=pick([16, 24, 40, 64]), q_rank=pick([8, 20, 64, 80]), base=pick([100.0, 1e4, 2.5e5]),
+                                 scale=pick([0.1, 0.25]), ff=ff, rot_dims=pick([rot_dim, rot_dim // 2 * 2 - 2 if rot_dim > 4 else rot_dim]),
+                                 layout=pick([None, None, "halves"])))
+        elif kind == "gla":
+            layers.append(gla(heads=pick([1, 2, 4, 6]), dim=pick([8, 16, 48, 72, 128]), vdim=pick([8, 16, 32, 40, 64]),
+                              tau=pick([1.0, 4.0, 16.0, 64.0]), ff=ff, decay_rank=pick([1, 4, 16])))
+        else:
+            kv = pick([1, 2, 4])
+            dim = pick([8, 16, 32, 48, 128])
+            layers.append(window(heads=kv * pick([1, 2, 4, 8]), kv_heads=kv, dim=dim, vdim=pick([8, 16, 32, 64, 128, 20]),
+                                 size=pick([1, 5, 16, 40, 64, 300]), keep_first=pick([0, 1, 6, 20]), base=pick([100.0, 2e4]),
+                                 rot_dims=pick([dim, dim // 2, 4]), scale=pick([0.09, 0.2]), ff=ff,
+                                 layout=pick([None, None, "halves"]), mask=pick([True, True, True, False])))
+    loop = None
+    if pick([True, True, False]):
+        a = pick(list(range(n)))
+        loop = (a, pick(list(range(a + 1, n + 1))), pick([1, 2, 3]))
+    return config(layers, width=pick([48, 64, 80, 128]), vocab=pick([50, 96, 257]), eps=pick([1e-5, 1e-6]),
+                  scale=pick([1.0, 8.0, 12.0]), cap=pick([0.0, 15.0, 30.0]), loop=loop)
+
+
+@pytest.mark.parametrize("seed", list(range(12)))
+def test_configurations_drawn_at_random(seed):
+    """what a checkpoint's config.json may say, drawn at random: whole prompt, prompt then single tokens, portions"""
+    cfg = random_config(100 + seed)
+    w = O.random_model(cfg, seed=200 + seed)
+    ids = tokens(75, cfg["vocab"], 300 + seed)
+    ref, _ = O.forward(cfg, w, ids)
+    for dtype in (torch.float32, torch.bfloat16):
+        for cuts in ([75], [50] + [1] * 25, [37, 2, 3, 1, 1, 14, 2]):
+            eng = make_engine(cfg, w, dtype=dtype, max_tokens=128, page_size=8)
+            slot = eng.open_sequence()
+            got = feed(eng, slot, ids, cuts)
+            if dtype == torch.float32:
+                assert rel_err(got, ref)[1] < 3e-4, (cfg, cuts)
+            else:
+                assert rel_err(got, ref)[0] < 8e-2, (cfg, cuts)
+            close(eng)
+
+
 # ------------------------------------------------------------------------------------------------ bf16 engine
 @pytest.mark.parametrize("tc", [1, 0], ids=["tcgen05", "cuda-cores"])
 @pytest.mark.parametrize("cfg_dict", [SMALL, ODD], ids=["small", "odd"])
