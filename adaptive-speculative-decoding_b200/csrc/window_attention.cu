@@ -25,8 +25,15 @@ namespace {
 __device__ __forceinline__ int warp_of(unsigned tid) { return (int)(tid >> 5); }
 
 __device__ __forceinline__ long long wcache_row(const PagedRows& c, int slot, int pos) {
-    const int page = c.page_table[(long long)slot * c.max_pages + pos / c.page_size];
-    return (long long)page * c.page_size + pos % c.page_size;
+    int pi, in_page;
+    if ((c.page_size & (c.page_size - 1)) == 0) {      // a power of two: shift and mask instead of a division
+        pi = pos >> (__ffs(c.page_size) - 1);
+        in_page = pos & (c.page_size - 1);
+    } else {
+        pi = pos / c.page_size;
+        in_page = pos - pi * c.page_size;
+    }
+    return (long long)c.page_table[(long long)slot * c.max_pages + pi] * c.page_size + in_page;
 }
 
 // turns the first n coordinates of src by angle pos * freq[pair] (sign -1 turns back); returns coordinate i
@@ -237,10 +244,13 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
                                                        int nsplit, float* ws_o, float* ws_ml, int q_alloc) {
     extern __shared__ __align__(16) unsigned char smraw[];
     const int LDQ = d.dk + 8, LDV = d.dv + 8;   // bf16 elements; 16 bytes of padding keep ldmatrix rows on distinct banks
-    __nv_bfloat16* Qh = reinterpret_cast<__nv_bfloat16*>(smraw);   // [q_alloc][LDQ]: 64 rows, or 16 for single-token steps
-    __nv_bfloat16* Ql = Qh + q_alloc * LDQ;
-    __nv_bfloat16* Ks = Ql + q_alloc * LDQ;                        // [STAGES][64][LDQ]
+    // queries: [q_alloc][LDQ] twice (64 rows, or 16 for single-token steps); q_alloc == 0: the 16 rows of a single-token
+    // step only pass through shared memory on their way into registers and borrow the last key buffer, which the first
+    // iteration of the tile loop fills
+    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw) + 2 * q_alloc * LDQ;   // [STAGES][64][LDQ]
     __nv_bfloat16* Vs = Ks + STAGES * WM_KEYS * LDQ;               // [STAGES][64][LDV]
+    __nv_bfloat16* Qh = q_alloc ? reinterpret_cast<__nv_bfloat16*>(smraw) : Ks + (STAGES - 1) * WM_KEYS * LDQ;
+    __nv_bfloat16* Ql = Qh + (q_alloc ? q_alloc : 16) * LDQ;
     float* stage = reinterpret_cast<float*>(Ks);                   // [64][dv] once the last tile is consumed
     float* stage_ml = stage + WM_ROWS * d.dv;                      // [64][2]: maximum and sum of every warp's share
     const int group = d.heads / d.kv_heads;
@@ -339,6 +349,7 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
                 ldsm_x4((uint32_t)__cvta_generic_to_shared(Ql + qoff), ql[k8]);
             }
         }
+        if (!q_alloc) __syncthreads();   // every warp has its fragments before the borrowed buffer is filled with keys
     }
     for (int it = 0; it < ntiles; ++it) {
         if (it + STAGES - 1 < ntiles) load_tile((it + STAGES - 1) % STAGES, it + STAGES - 1, next_off);
@@ -409,7 +420,8 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             txB = fmaxf(txB, __shfl_xor_sync(0xffffffffu, txB, 2));
             const float nA_ = fmaxf(mA, txA), nB_ = fmaxf(mB, txB);
             const float sA = nA_ == -INFINITY ? 0.f : nA_, sB = nB_ == -INFINITY ? 0.f : nB_;   // nothing seen yet: weights 0
-            const float cA = __expf(mA - sA), cB = __expf(mB - sB);
+            // (rows beyond the CTA's own keep factor 1, so that they never ask for a rescale)
+            const float cA = okA ? __expf(mA - sA) : 1.f, cB = okB ? __expf(mB - sB) : 1.f;
             mA = nA_, mB = nB_;
             float sumA = 0.f, sumB = 0.f;
 #pragma unroll
@@ -595,7 +607,8 @@ int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nse
         const long long ctas = (long long)nseq * d.kv_heads;
         const long long keys = (long long)(d.window < max_kv_len ? d.window : max_kv_len) + d.keep_first;
         const int tiles = (int)((keys + WM_KEYS - 1) / WM_KEYS) + 1;
-        while (nsplit < 8 && ctas * nsplit < 2LL * sms && tiles >= 4 * nsplit) nsplit *= 2;
+        // as many shares as still fit one wave of two CTAs per SM: a second, partly filled wave would cost more than it saves
+        while (nsplit < 8 && ctas * nsplit * 2 <= 2LL * sms && tiles >= 4 * nsplit) nsplit *= 2;
         while (nsplit > 1 && ((long long)ix.M * d.heads * nsplit > ws.rows || (long long)ix.M * d.heads * nsplit * d.dv > ws.o_elems))
             nsplit /= 2;
     }
@@ -603,8 +616,11 @@ int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nse
     // single-token steps are bound by the latency of the key/value stream: four tiles in flight when the grid leaves an
     // SM to one CTA anyway, two (and two CTAs per SM) otherwise
     const bool single = max_qlen * group <= 16;          // every CTA has at most 16 rows: a small query buffer, more tiles in flight
-    const int stages = !single ? 2 : ((long long)grid.x * grid.y * grid.z <= sms ? 4 : 3);
-    const int q_alloc = single ? 16 : WM_ROWS;
+    // ... and when the key size lets the query fragments live in registers, no query buffer at all: with two tiles in
+    // flight three CTAs then share an SM
+    const bool q_in_regs = single && d.dk <= 128;
+    const int stages = !single ? 2 : ((long long)grid.x * grid.y * grid.z <= sms ? 4 : (q_in_regs ? 2 : 3));
+    const int q_alloc = q_in_regs ? 0 : (single ? 16 : WM_ROWS);
     const size_t smem = (size_t)(2 * q_alloc * (d.dk + 8) + stages * WM_KEYS * (d.dk + 8 + d.dv + 8)) * 2;
     if (smem > (size_t)kMaxSmem) return set_error("windowed attention: head sizes %d / %d do not fit shared memory", d.dk, d.dv);
     if (grid.y > 65535 || grid.z > 65535) return set_error("windowed attention: too many sequences or heads");
@@ -622,6 +638,8 @@ int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nse
             ASD_WM_LAUNCH(N, 4, true)   \
         else if (stages == 3)           \
             ASD_WM_LAUNCH(N, 3, true)   \
+        else if (single)                \
+            ASD_WM_LAUNCH(N, 2, true)   \
         else                            \
             ASD_WM_LAUNCH(N, 2, false)  \
     }
