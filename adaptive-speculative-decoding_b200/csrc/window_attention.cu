@@ -237,13 +237,16 @@ __device__ __forceinline__ void split2(float x, __nv_bfloat16& hi, __nv_bfloat16
 // STAGES key/value tiles are in flight.  When the CTA has at most 16 rows (single-token steps), all four warps take
 // those rows and a quarter of every tile's keys each, and their partial results are merged at the end.
 // SINGLE: every CTA of the launch is of that kind (single-token steps); the query fragments then stay in registers.
-template <int NV, int STAGES, bool SINGLE>   // value column tiles of 8: dv <= 8 * NV
+// SQ: key and value size are both exactly 8 * NV (64 or 128 in practice): every loop bound and row stride is then a
+// compile-time constant.
+template <int NV, int STAGES, bool SINGLE, bool SQ>   // value column tiles of 8: dv <= 8 * NV
 __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* cu_q, const int* seq_slot, int TQ,
                                                        const float* q, long long ldq, WindowDims d, const float* sink,
                                                        const float* freq_v, PagedRows cache, void* out, int of32,
                                                        int nsplit, float* ws_o, float* ws_ml, int q_alloc) {
     extern __shared__ __align__(16) unsigned char smraw[];
-    const int LDQ = d.dk + 8, LDV = d.dv + 8;   // bf16 elements; 16 bytes of padding keep ldmatrix rows on distinct banks
+    const int dk = SQ ? 8 * NV : d.dk, dv = SQ ? 8 * NV : d.dv;
+    const int LDQ = dk + 8, LDV = dv + 8;   // bf16 elements; 16 bytes of padding keep ldmatrix rows on distinct banks
     // queries: [q_alloc][LDQ] twice (64 rows, or 16 for single-token steps); q_alloc == 0: the 16 rows of a single-token
     // step only pass through shared memory on their way into registers and borrow the last key buffer, which the first
     // iteration of the tile loop fills
@@ -252,7 +255,7 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
     __nv_bfloat16* Qh = q_alloc ? reinterpret_cast<__nv_bfloat16*>(smraw) : Ks + (STAGES - 1) * WM_KEYS * LDQ;
     __nv_bfloat16* Ql = Qh + (q_alloc ? q_alloc : 16) * LDQ;
     float* stage = reinterpret_cast<float*>(Ks);                   // [64][dv] once the last tile is consumed
-    float* stage_ml = stage + WM_ROWS * d.dv;                      // [64][2]: maximum and sum of every warp's share
+    float* stage_ml = stage + WM_ROWS * dv;                      // [64][2]: maximum and sum of every warp's share
     const int group = d.heads / d.kv_heads;
     const int seq = blockIdx.y, g = blockIdx.z;
     const int split = blockIdx.x % nsplit;       // this CTA's share of the key tiles (single-token steps only)
@@ -272,8 +275,8 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
     // queries as hi + lo bf16 terms
     const int q_rows = n_rows <= 16 ? 16 : WM_ROWS;      // rows the products read (the rest of a single-token tile is unused)
     for (int r = warp; r < q_rows; r += 4) {
-        const float* src = r < n_rows ? q + (long long)(t0 + r / group) * ldq + (long long)(g * group + r % group) * d.dk : nullptr;
-        for (int c = lane; c < d.dk; c += 32) {
+        const float* src = r < n_rows ? q + (long long)(t0 + r / group) * ldq + (long long)(g * group + r % group) * dk : nullptr;
+        for (int c = lane; c < dk; c += 32) {
             __nv_bfloat16 hi, lw;
             split2(src ? src[c] : 0.f, hi, lw);
             Qh[r * LDQ + c] = hi;
@@ -281,8 +284,8 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
         }
     }
     const __nv_bfloat16* pool = reinterpret_cast<const __nv_bfloat16*>(cache.pool);
-    const int nk = d.kv_heads * d.dk, rowlen = nk + d.kv_heads * d.dv;
-    const int ck = d.dk >> 3, cpr = (d.dk + d.dv) >> 3;
+    const int nk = d.kv_heads * dk, rowlen = nk + d.kv_heads * dv;
+    const int ck = dk >> 3, cpr = (dk + dv) >> 3;
     auto tile_range = [&](int i, int& j0, int& j_end) {
         i += tile0;
         if (i < nA) {
@@ -311,8 +314,8 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
         const int r = tid >> 1;
         const bool ok = j0 + r < j_end;
         const __nv_bfloat16* src = pool + row_off;
-        const __nv_bfloat16* ksrc = src + (long long)g * d.dk;
-        const __nv_bfloat16* vsrc = src + nk + (long long)g * d.dv;
+        const __nv_bfloat16* ksrc = src + (long long)g * dk;
+        const __nv_bfloat16* vsrc = src + nk + (long long)g * dv;
         for (int cc = tid & 1; cc < ck; cc += 2)
             cp_async16((uint32_t)__cvta_generic_to_shared(kd + r * LDQ + cc * 8), ksrc + cc * 8, ok);
         for (int cc = tid & 1; cc < cpr - ck; cc += 2)
@@ -329,7 +332,7 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
     float o[NV][4];
 #pragma unroll
     for (int i = 0; i < NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    const int nvt = d.dv >> 3;
+    const int nvt = SQ ? NV : dv >> 3;
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) {
         if (i < ntiles) load_tile(i, i, lookup(i));
@@ -338,12 +341,12 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
     long long next_off = lookup(STAGES - 1);
     // single-token steps: the 16 query rows are the same for every tile and warp, their fragments are loaded once
     uint32_t qh[SINGLE ? 8 : 1][4], ql[SINGLE ? 8 : 1][4];
-    const bool q_regs = SINGLE && d.dk <= 128;
+    const bool q_regs = SINGLE && dk <= 128;
     if (q_regs) {
         __syncthreads();   // the queries are in place
 #pragma unroll
         for (int k8 = 0; k8 < (SINGLE ? 8 : 1); ++k8) {
-            if (k8 * 16 < d.dk) {
+            if (k8 * 16 < dk) {
                 const int qoff = (lane & 15) * LDQ + k8 * 16 + (lane >> 4) * 8;
                 ldsm_x4((uint32_t)__cvta_generic_to_shared(Qh + qoff), qh[k8]);
                 ldsm_x4((uint32_t)__cvta_generic_to_shared(Ql + qoff), ql[k8]);
@@ -368,7 +371,7 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             if (q_regs) {
 #pragma unroll
                 for (int k8 = 0; k8 < (SINGLE ? 8 : 1); ++k8) {
-                    if (k8 * 16 < d.dk) {
+                    if (k8 * 16 < dk) {
                         uint32_t b[4];
                         ldsm_x4((uint32_t)__cvta_generic_to_shared(kb + ((lane & 7) + ((lane >> 4) & 1) * 8) * LDQ + k8 * 16 +
                                                                     ((lane >> 3) & 1) * 8), b);
@@ -379,7 +382,7 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
                     }
                 }
             } else
-            for (int ks = 0; ks < d.dk; ks += 16) {
+            for (int ks = 0; ks < dk; ks += 16) {
                 uint32_t ah[4], al[4];
                 const int qoff = (row0 + (lane & 15)) * LDQ + ks + (lane >> 4) * 8;
                 ldsm_x4((uint32_t)__cvta_generic_to_shared(Qh + qoff), ah);
@@ -396,8 +399,22 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
                     mma_bf16(s[2 * np + 1], al, b[2], b[3]);
                 }
             }
-            // mask, running maxima
+            // mask, running maxima.  Steps of one or a few tokens: most of a warp's 16-key shares lie wholly inside every
+            // row's window (or the kept range) and before every row's position: those take the scale alone
             float txA = -INFINITY, txB = -INFINITY;
+            const int k_lo = j0 + key0, k_hi = k_lo + 15;
+            const bool whole = SINGLE && k_hi < j_end && k_hi <= p_first && (p_last - k_lo < d.window || k_hi < d.keep_first);
+            if (whole) {
+#pragma unroll
+                for (int nt = 0; nt < 2 * NP; ++nt) {
+                    s[nt][0] = okA ? s[nt][0] * d.scale : -INFINITY;
+                    s[nt][1] = okA ? s[nt][1] * d.scale : -INFINITY;
+                    s[nt][2] = okB ? s[nt][2] * d.scale : -INFINITY;
+                    s[nt][3] = okB ? s[nt][3] * d.scale : -INFINITY;
+                    txA = fmaxf(txA, fmaxf(s[nt][0], s[nt][1]));
+                    txB = fmaxf(txB, fmaxf(s[nt][2], s[nt][3]));
+                }
+            } else {
 #pragma unroll
             for (int nt = 0; nt < 2 * NP; ++nt) {
                 if (nt >= 2 * npw) break;
@@ -413,6 +430,7 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
                     else
                         txB = fmaxf(txB, v);
                 }
+            }
             }
             txA = fmaxf(txA, __shfl_xor_sync(0xffffffffu, txA, 1));
             txA = fmaxf(txA, __shfl_xor_sync(0xffffffffu, txA, 2));
@@ -488,8 +506,8 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
         for (int i = 0; i < NV; ++i) {
             if (i < nvt) {
                 const int c = i * 8 + (lane & 3) * 2;
-                float* sa = stage + (warp * 16 + (lane >> 2)) * d.dv + c;
-                float* sb = sa + 8 * d.dv;
+                float* sa = stage + (warp * 16 + (lane >> 2)) * dv + c;
+                float* sb = sa + 8 * dv;
                 sa[0] = o[i][0], sa[1] = o[i][1];
                 sb[0] = o[i][2], sb[1] = o[i][3];
             }
@@ -497,8 +515,8 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
         __syncthreads();
         if (nsplit > 1) {
             // this CTA saw a share of the keys: its merged maximum, sum and unnormalised result wait for the combine kernel
-            for (int i = tid; i < n_rows * d.dv; i += 128) {
-                const int r = i / d.dv, c = i % d.dv;
+            for (int i = tid; i < n_rows * dv; i += 128) {
+                const int r = i / dv, c = i % dv;
                 float mx = -INFINITY;
 #pragma unroll
                 for (int w = 0; w < 4; ++w) mx = fmaxf(mx, stage_ml[(w * 16 + r) * 2]);
@@ -507,16 +525,16 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
                 for (int w = 0; w < 4; ++w) {
                     const float f = mx == -INFINITY ? 0.f : expf(stage_ml[(w * 16 + r) * 2] - mx);
                     den += stage_ml[(w * 16 + r) * 2 + 1] * f;
-                    num += stage[(w * 16 + r) * d.dv + c] * f;
+                    num += stage[(w * 16 + r) * dv + c] * f;
                 }
                 const long long pair = ((long long)(t0 + r / group) * d.heads + g * group + r % group) * nsplit + split;
-                ws_o[pair * d.dv + c] = num;
+                ws_o[pair * dv + c] = num;
                 if (c == 0) ws_ml[pair * 2] = mx, ws_ml[pair * 2 + 1] = den;
             }
             return;
         }
-        for (int i = tid; i < n_rows * d.dv; i += 128) {
-            const int r = i / d.dv, c = i % d.dv;
+        for (int i = tid; i < n_rows * dv; i += 128) {
+            const int r = i / dv, c = i % dv;
             float mx = -INFINITY;
 #pragma unroll
             for (int w = 0; w < 4; ++w) mx = fmaxf(mx, stage_ml[(w * 16 + r) * 2]);
@@ -526,9 +544,9 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             for (int w = 0; w < 4; ++w) {
                 const float f = expf(stage_ml[(w * 16 + r) * 2] - mx);       // a share that saw no key: exp(-inf) = 0
                 den += stage_ml[(w * 16 + r) * 2 + 1] * f;
-                num += stage[(w * 16 + r) * d.dv + c] * f;
+                num += stage[(w * 16 + r) * dv + c] * f;
             }
-            stage[r * d.dv + c] = num / den;       // only this thread reads column c of row r's shares
+            stage[r * dv + c] = num / den;       // only this thread reads column c of row r's shares
         }
     } else {
     float invA = 1.f / lA, invB = 1.f / lB;
@@ -546,17 +564,17 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
     for (int i = 0; i < NV; ++i) {
         if (i < nvt) {
             const int c = i * 8 + (lane & 3) * 2;
-            if (okA) stage[rA * d.dv + c] = o[i][0] * invA, stage[rA * d.dv + c + 1] = o[i][1] * invA;
-            if (okB) stage[rB * d.dv + c] = o[i][2] * invB, stage[rB * d.dv + c + 1] = o[i][3] * invB;
+            if (okA) stage[rA * dv + c] = o[i][0] * invA, stage[rA * dv + c + 1] = o[i][1] * invA;
+            if (okB) stage[rB * dv + c] = o[i][2] * invB, stage[rB * dv + c + 1] = o[i][3] * invB;
         }
     }
     }
     __syncthreads();
-    for (int i = tid; i < n_rows * d.dv; i += 128) {
-        const int r = i / d.dv, c = i % d.dv;
+    for (int i = tid; i < n_rows * dv; i += 128) {
+        const int r = i / dv, c = i % dv;
         const long long m = t0 + r / group;
-        stx(out, (m * d.heads + g * group + r % group) * d.dv + c, of32,
-            turned(stage + r * d.dv, c, d.dv, d.interleaved, (float)(p_first + r / group), freq_v, -1.f));
+        stx(out, (m * d.heads + g * group + r % group) * dv + c, of32,
+            turned(stage + r * dv, c, dv, d.interleaved, (float)(p_first + r / group), freq_v, -1.f));
     }
 }
 
@@ -624,28 +642,30 @@ int launch_mma(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nse
     const size_t smem = (size_t)(2 * q_alloc * (d.dk + 8) + stages * WM_KEYS * (d.dk + 8 + d.dv + 8)) * 2;
     if (smem > (size_t)kMaxSmem) return set_error("windowed attention: head sizes %d / %d do not fit shared memory", d.dk, d.dv);
     if (grid.y > 65535 || grid.z > 65535) return set_error("windowed attention: too many sequences or heads");
-#define ASD_WM_LAUNCH(N, S, G)                                                                                       \
+#define ASD_WM_LAUNCH(N, S, G, Q)                                                                                    \
     {                                                                                                                \
-        auto fn = window_attn_mma<N, S, G>;                                                                           \
+        auto fn = window_attn_mma<N, S, G, Q>;                                                                           \
         static PerDeviceOnce once;   /* the attribute is set once per device: a host call per launch costs microseconds */ \
         if (once.need()) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem)); \
         fn<<<grid, 128, smem, stream>>>(ix, cu_q, seq_slot, TQ, q, ldq, d, sink, freq_v, cache, out, of32, nsplit,   \
                                         ws.o, ws.ml, q_alloc);                                                       \
     }
-#define ASD_WM_CASE(N)            \
+#define ASD_WM_CASE(N, Q)         \
     {                             \
-        if (stages == 4)                \
-            ASD_WM_LAUNCH(N, 4, true)   \
-        else if (stages == 3)           \
-            ASD_WM_LAUNCH(N, 3, true)   \
-        else if (single)                \
-            ASD_WM_LAUNCH(N, 2, true)   \
-        else                            \
-            ASD_WM_LAUNCH(N, 2, false)  \
+        if (stages == 4)                   \
+            ASD_WM_LAUNCH(N, 4, true, Q)   \
+        else if (stages == 3)              \
+            ASD_WM_LAUNCH(N, 3, true, Q)   \
+        else if (single)                   \
+            ASD_WM_LAUNCH(N, 2, true, Q)   \
+        else                               \
+            ASD_WM_LAUNCH(N, 2, false, false) /* prompts: the constant sizes cost registers and measured 7 % slower */ \
     }
-    if (d.dv <= 32) ASD_WM_CASE(4)
-    else if (d.dv <= 64) ASD_WM_CASE(8)
-    else ASD_WM_CASE(16)
+    if (d.dk == 128 && d.dv == 128) ASD_WM_CASE(16, true)
+    else if (d.dk == 64 && d.dv == 64) ASD_WM_CASE(8, true)
+    else if (d.dv <= 32) ASD_WM_CASE(4, false)
+    else if (d.dv <= 64) ASD_WM_CASE(8, false)
+    else ASD_WM_CASE(16, false)
 #undef ASD_WM_CASE
 #undef ASD_WM_LAUNCH
     count_launch(1);
