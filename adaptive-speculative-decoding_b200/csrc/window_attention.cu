@@ -381,22 +381,23 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
                         mma_bf16(s[1], ql[k8], b[2], b[3]);
                     }
                 }
-            } else
-            for (int ks = 0; ks < dk; ks += 16) {
-                uint32_t ah[4], al[4];
-                const int qoff = (row0 + (lane & 15)) * LDQ + ks + (lane >> 4) * 8;
-                ldsm_x4((uint32_t)__cvta_generic_to_shared(Qh + qoff), ah);
-                ldsm_x4((uint32_t)__cvta_generic_to_shared(Ql + qoff), al);
+            } else {
+                for (int ks = 0; ks < dk; ks += 16) {
+                    uint32_t ah[4], al[4];
+                    const int qoff = (row0 + (lane & 15)) * LDQ + ks + (lane >> 4) * 8;
+                    ldsm_x4((uint32_t)__cvta_generic_to_shared(Qh + qoff), ah);
+                    ldsm_x4((uint32_t)__cvta_generic_to_shared(Ql + qoff), al);
 #pragma unroll
-                for (int np = 0; np < NP; ++np) {
-                    if (np >= npw) break;
-                    uint32_t b[4];
-                    ldsm_x4((uint32_t)__cvta_generic_to_shared(kb + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LDQ + ks +
-                                                                ((lane >> 3) & 1) * 8), b);
-                    mma_bf16(s[2 * np], ah, b[0], b[1]);
-                    mma_bf16(s[2 * np], al, b[0], b[1]);
-                    mma_bf16(s[2 * np + 1], ah, b[2], b[3]);
-                    mma_bf16(s[2 * np + 1], al, b[2], b[3]);
+                    for (int np = 0; np < NP; ++np) {
+                        if (np >= npw) break;
+                        uint32_t b[4];
+                        ldsm_x4((uint32_t)__cvta_generic_to_shared(kb + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LDQ + ks +
+                                                                    ((lane >> 3) & 1) * 8), b);
+                        mma_bf16(s[2 * np], ah, b[0], b[1]);
+                        mma_bf16(s[2 * np], al, b[0], b[1]);
+                        mma_bf16(s[2 * np + 1], ah, b[2], b[3]);
+                        mma_bf16(s[2 * np + 1], al, b[2], b[3]);
+                    }
                 }
             }
             // mask, running maxima.  Steps of one or a few tokens: most of a warp's 16-key shares lie wholly inside every
@@ -416,21 +417,21 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
                 }
             } else {
 #pragma unroll
-            for (int nt = 0; nt < 2 * NP; ++nt) {
-                if (nt >= 2 * npw) break;
+                for (int nt = 0; nt < 2 * NP; ++nt) {
+                    if (nt >= 2 * npw) break;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int kp = j0 + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                    const int p = e < 2 ? pA : pB;
-                    const bool seen = (e < 2 ? okA : okB) && kp < j_end && kp <= p && (p - kp < d.window || kp < d.keep_first);
-                    const float v = seen ? s[nt][e] * d.scale : -INFINITY;
-                    s[nt][e] = v;
-                    if (e < 2)
-                        txA = fmaxf(txA, v);
-                    else
-                        txB = fmaxf(txB, v);
+                    for (int e = 0; e < 4; ++e) {
+                        const int kp = j0 + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                        const int p = e < 2 ? pA : pB;
+                        const bool seen = (e < 2 ? okA : okB) && kp < j_end && kp <= p && (p - kp < d.window || kp < d.keep_first);
+                        const float v = seen ? s[nt][e] * d.scale : -INFINITY;
+                        s[nt][e] = v;
+                        if (e < 2)
+                            txA = fmaxf(txA, v);
+                        else
+                            txB = fmaxf(txB, v);
+                    }
                 }
-            }
             }
             txA = fmaxf(txA, __shfl_xor_sync(0xffffffffu, txA, 1));
             txA = fmaxf(txA, __shfl_xor_sync(0xffffffffu, txA, 2));
@@ -549,25 +550,25 @@ __global__ void __launch_bounds__(128) window_attn_mma(SeqIndex ix, const int* c
             stage[r * dv + c] = num / den;       // only this thread reads column c of row r's shares
         }
     } else {
-    float invA = 1.f / lA, invB = 1.f / lB;
-    if (sink) {   // one more term of the denominator, without a value
-        if (okA) {
-            const float sk = sink[g * group + rA % group], mf = fmaxf(mA, sk), so = expf(mA - mf);
-            invA = so / (lA * so + expf(sk - mf));
+        float invA = 1.f / lA, invB = 1.f / lB;
+        if (sink) {   // one more term of the denominator, without a value
+            if (okA) {
+                const float sk = sink[g * group + rA % group], mf = fmaxf(mA, sk), so = expf(mA - mf);
+                invA = so / (lA * so + expf(sk - mf));
+            }
+            if (okB) {
+                const float sk = sink[g * group + rB % group], mf = fmaxf(mB, sk), so = expf(mB - mf);
+                invB = so / (lB * so + expf(sk - mf));
+            }
         }
-        if (okB) {
-            const float sk = sink[g * group + rB % group], mf = fmaxf(mB, sk), so = expf(mB - mf);
-            invB = so / (lB * so + expf(sk - mf));
-        }
-    }
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        if (i < nvt) {
-            const int c = i * 8 + (lane & 3) * 2;
-            if (okA) stage[rA * dv + c] = o[i][0] * invA, stage[rA * dv + c + 1] = o[i][1] * invA;
-            if (okB) stage[rB * dv + c] = o[i][2] * invB, stage[rB * dv + c + 1] = o[i][3] * invB;
+        for (int i = 0; i < NV; ++i) {
+            if (i < nvt) {
+                const int c = i * 8 + (lane & 3) * 2;
+                if (okA) stage[rA * dv + c] = o[i][0] * invA, stage[rA * dv + c + 1] = o[i][1] * invA;
+                if (okB) stage[rB * dv + c] = o[i][2] * invB, stage[rB * dv + c + 1] = o[i][3] * invB;
+            }
         }
-    }
     }
     __syncthreads();
     for (int i = tid; i < n_rows * dv; i += 128) {
