@@ -240,7 +240,7 @@ def sized_config(width: int, n_layers: int, heads: int, vocab: int = 32768, dim:
     ff = ff if ff is not None else 4 * width
     lat = RivetarLayer(type="latent_attention", heads=heads, dim=dim, vdim=dim, rot_dim=dim // 2, kv_rank=512,
                        q_rank=max(256, width // 2), rot_dims=dim // 2, scale=1.0 / math.sqrt(dim + dim // 2), ff=ff)
-    gla = RivetarLayer(type="gla", heads=heads, dim=dim, vdim=dim, decay_rank=16, tau=16.0, ff=ff)
+    gla = RivetarLayer(type="gla", heads=heads, dim=dim, vdim=dim, decay_rank=32, tau=8.0, ff=ff)
     att = RivetarLayer(type="attention", heads=heads, kv_heads=max(1, heads // 4), dim=dim, vdim=dim, rot_dims=dim,
                        window=window, keep_first=keep_first, scale=1.0 / math.sqrt(dim), ff=ff)
     return RivetarConfig(width=width, vocab_size=vocab, layers=[(lat, gla, att)[i % 3] for i in range(n_layers)],

@@ -218,7 +218,7 @@ def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
                       p + "mix.o": (D, H * m["vdim"])})
         elif e["type"] == "gla":
             H = m["heads"]
-            low = m.get("decay_rank", 16)
+            low = m.get("decay_rank", 8)
             s.update({p + "mix.q": (H * m["dim"], D), p + "mix.k": (H * m["dim"], D), p + "mix.v": (H * m["vdim"], D),
                       p + "mix.g": (H * m["vdim"], D), p + "mix.o": (D, H * m["vdim"]), p + "mix.norm": (m["vdim"],),
                       p + "mix.a1": (low, D), p + "mix.a2": (H * m["dim"], low), p + "mix.a2.b": (H * m["dim"],)})

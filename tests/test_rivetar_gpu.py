@@ -440,17 +440,17 @@ def random_config(seed):
         if kind == "latent":
             rot_dim = pick([4, 8, 16, 32])
             layers.append(latent(heads=pick([1, 2, 4, 5]), dim=pick([8, 16, 24, 64]), rot_dim=rot_dim, vdim=pick([8, 16, 20, 48]),
-                                 kv_rank=pick([16, 24, 40, 64]), q_rank=pick([8, 20, 64, 80]), base=pick([100.0, 1e4, 2.5e5]),
+                                 kv_rank=pick([16, 24, 40, 64]), q_rank=pick([8, 20, 64, 72]), base=pick([100.0, 1e4, 3e5]),
                                  scale=pick([0.1, 0.25]), ff=ff, rot_dims=pick([rot_dim, rot_dim // 2 * 2 - 2 if rot_dim > 4 else rot_dim]),
                                  layout=pick([None, None, "halves"])))
         elif kind == "gla":
             layers.append(gla(heads=pick([1, 2, 4, 6]), dim=pick([8, 16, 48, 72, 128]), vdim=pick([8, 16, 32, 40, 64]),
-                              tau=pick([1.0, 4.0, 16.0, 64.0]), ff=ff, decay_rank=pick([1, 4, 16])))
+                              tau=pick([1.0, 4.0, 12.0, 64.0]), ff=ff, decay_rank=pick([1, 4, 12])))
         else:
             kv = pick([1, 2, 4])
             dim = pick([8, 16, 32, 48, 128])
             layers.append(window(heads=kv * pick([1, 2, 4, 8]), kv_heads=kv, dim=dim, vdim=pick([8, 16, 32, 64, 128, 20]),
-                                 size=pick([1, 5, 16, 40, 64, 300]), keep_first=pick([0, 1, 6, 20]), base=pick([100.0, 2e4]),
+                                 size=pick([1, 5, 16, 33, 64, 300]), keep_first=pick([0, 1, 5, 20]), base=pick([100.0, 3e4]),
                                  rot_dims=pick([dim, dim // 2, 4]), scale=pick([0.09, 0.2]), ff=ff,
                                  layout=pick([None, None, "halves"]), mask=pick([True, True, True, False])))
     loop = None
@@ -458,7 +458,7 @@ def random_config(seed):
         a = pick(list(range(n)))
         loop = (a, pick(list(range(a + 1, n + 1))), pick([1, 2, 3]))
     return config(layers, width=pick([48, 64, 80, 128]), vocab=pick([50, 96, 257]), eps=pick([1e-5, 1e-6]),
-                  scale=pick([1.0, 8.0, 12.0]), cap=pick([0.0, 15.0, 30.0]), loop=loop)
+                  scale=pick([1.0, 8.0, 11.0]), cap=pick([0.0, 14.0, 30.0]), loop=loop)
 
 
 @pytest.mark.parametrize("seed", list(range(12)))
@@ -499,7 +499,7 @@ def test_bf16_engine_on_sizes_that_fill_tensor_core_tiles():
     tensor-bound CTA-pair GEMM"""
     cfg = config([latent(heads=4, dim=64, rot_dim=32, vdim=64, kv_rank=128, q_rank=64, ff=256),
                   gla(heads=2, dim=64, vdim=64, tau=16.0, ff=128, decay_rank=16),
-                  window(heads=4, kv_heads=2, dim=64, vdim=64, size=40, keep_first=4, rot_dims=64, scale=0.125, ff=128)],
+                  window(heads=4, kv_heads=2, dim=64, vdim=64, size=37, keep_first=4, rot_dims=64, scale=0.125, ff=128)],
                  width=256, vocab=512, loop=(1, 3, 2))
     w = O.random_model(cfg, seed=33)
     ids = tokens(300, 512, 34)
