@@ -1,4 +1,5 @@
-// Batched / grouped linear layer on the CUDA cores: fp32 FMA accumulation in increasing k, any shape, any of
+// Batched / grouped linear layer on the CUDA cores: fp32 FMA accumulation in increasing k (slices of 16 summed on their
+// own, then added up in order), any shape, any of
 // {bf16, fp32} for the activations, the weights and the result.  It is the arithmetic of the fp32 engines (no tensor
 // core has a true fp32 mode) and the fallback of the bf16 engines for shapes outside the tcgen05 GEMM's contract.
 // 64 x 64 output tile per CTA, 16-deep k slices through shared memory, 4 x 4 results per thread.
@@ -59,6 +60,13 @@ __global__ void __launch_bounds__(256) simt_linear_kernel(SimtLinear L) {
             Ws[lk][lr + 16 * i] = (n < L.N && k < L.K) ? ldf(W + (long long)n * L.ldw + k) : 0.f;
         }
         __syncthreads();
+        // a slice's 16 products are summed on their own and then added to the total: the rounding error of a long sum
+        // grows with sqrt(16) + sqrt(K / 16) instead of sqrt(K) steps, still in one fixed order
+        float part[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < TK; ++kk) {
             float a[4], b[4];
@@ -69,8 +77,12 @@ __global__ void __launch_bounds__(256) simt_linear_kernel(SimtLinear L) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) part[i][j] = fmaf(a[i], b[j], part[i][j]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
         __syncthreads();
     }
 #pragma unroll
